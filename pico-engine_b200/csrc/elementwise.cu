@@ -1,0 +1,189 @@
+// Embedding lookup, RMSNorm, SwiGLU and the rotary encoding fused with the write of keys
+// and values into the paged cache.  All arithmetic is float32; only loads and stores
+// convert.  The residual stream is float32 in both engine dtypes.
+//
+// pico-engine's counterparts are the Triton kernels _rmsnorm_fwd, _rope_fwd and
+// _silu_mul_fwd (src/pico_engine/kernels.py:14-23, 37-47, 62-74), the torch gather at
+// src/pico_engine/model.py:152 and the index_copy_ cache write at model.py:190-196.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);          // the host refuses such ids; never read outside the table
+    const TW* row = table + (size_t)id * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f(row[i]);
+}
+
+extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, float* out, int T, int H, int V,
+                        void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == PE_F32) embed_kernel<float><<<T, 256, 0, s>>>((const float*)table, ids, out, H, V);
+    else if (table_dtype == PE_BF16) embed_kernel<bf16><<<T, 256, 0, s>>>((const bf16*)table, ids, out, H, V);
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per output row.  `rows_index` (may be null) picks the input row of each output
+// row, so the final norm runs only on the rows whose logits are wanted.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
+                               const void* __restrict__ w, int w_dtype, float eps, TO* __restrict__ out, int H) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows_index ? rows_index[r] : r) * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(xr[i] * rstd * load_as_f(w, w_dtype, i));
+}
+
+extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, int w_dtype, float eps, void* out,
+                          int out_dtype, int rows, int H, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 2048 ? 512 : 256;
+    if (out_dtype == PE_F32) rmsnorm_kernel<float><<<rows, threads, 0, s>>>(x, rows_index, w, w_dtype, eps, (float*)out, H);
+    else if (out_dtype == PE_BF16) rmsnorm_kernel<bf16><<<rows, threads, 0, s>>>(x, rows_index, w, w_dtype, eps, (bf16*)out, H);
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// gu is [T, 2I]: gate in the first I columns, up in the last I.  out[t, i] = silu(gate) * up.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, i = idx % I;
+        const float g = to_f(gu[t * 2 * I + i]), u = to_f(gu[t * 2 * I + I + i]);
+        const float sig = 1.0f / (1.0f + expf(-g));
+        out[idx] = from_f<T>(g * sig * u);
+    }
+}
+
+extern "C" int pe_swiglu(const void* gu, void* out, int dtype, int T, int I, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)T * I;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == PE_F32) swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, total);
+    else if (dtype == PE_BF16) swiglu_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- residual add
+// x[t, :] += y[t, :] in float32 (y in either dtype): the epilogue of a library matrix product.
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ y, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] += to_f(y[i]);
+}
+
+extern "C" int pe_residual_add(float* x, const void* y, int y_dtype, long long total, void* stream) {
+    if (total <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (y_dtype == PE_F32) residual_add_kernel<float><<<blocks, 256, 0, s>>>(x, (const float*)y, (size_t)total);
+    else if (y_dtype == PE_BF16) residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(x, (const bf16*)y, (size_t)total);
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- bias add (library matrix product epilogue)
+template <typename T>
+__global__ void bias_add_kernel(T* __restrict__ y, const void* __restrict__ bias, int bias_dtype, int N, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = from_f<T>(to_f(y[i]) + load_as_f(bias, bias_dtype, i % N));
+}
+
+extern "C" int pe_bias_add(void* y, int dtype, const void* bias, int bias_dtype, int M, int N, void* stream) {
+    if (M <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)M * N;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == PE_F32) bias_add_kernel<float><<<blocks, 256, 0, s>>>((float*)y, bias, bias_dtype, N, total);
+    else if (dtype == PE_BF16) bias_add_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)y, bias, bias_dtype, N, total);
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- rotary encoding + cache write
+// qkv is [T, (n_q + 2 n_kv) * hd]: query heads, key heads, value heads.  Query and key heads
+// are rotated in place (pairs j, j + hd/2; cos/sin are float32 tables [positions, hd/2];
+// null tables leave them as they are).  Rotated keys and the values are then written to the
+// paged cache at (page of the token's sequence, position % PE_PAGE) when `store` is set.
+// Pool layout: [page][kv head][PE_PAGE][hd].
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, int n_q, int n_kv, int hd,
+                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                  const int* __restrict__ tok_pos, const int* __restrict__ tok_row,
+                                  T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                  const int* __restrict__ block_table, int table_stride, int store) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = hd >> 1;
+    T* row = qkv + (size_t)t * (n_q + 2 * n_kv) * hd;
+    size_t cache_base = 0;
+    bool do_store = false;
+    if (store) {
+        const int page = block_table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+        do_store = page >= 0;
+        cache_base = (size_t)page * n_kv * PE_PAGE * hd + (size_t)(pos % PE_PAGE) * hd;
+    }
+    const int n_rot = (n_q + n_kv) * half;
+    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+        const int head = idx / half, j = idx % half;
+        T* p = row + (size_t)head * hd;
+        float a = to_f(p[j]), b = to_f(p[j + half]);
+        if (cos_t) {
+            const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+            const float ra = a * c - b * s, rb = a * s + b * c;
+            a = ra; b = rb;
+            p[j] = from_f<T>(a); p[j + half] = from_f<T>(b);
+        }
+        if (do_store && head >= n_q) {
+            T* dst = k_pool + cache_base + (size_t)(head - n_q) * PE_PAGE * hd;
+            dst[j] = from_f<T>(a); dst[j + half] = from_f<T>(b);
+        }
+    }
+    if (do_store) {
+        const T* v = row + (size_t)(n_q + n_kv) * hd;
+        for (int idx = threadIdx.x; idx < n_kv * hd; idx += blockDim.x) {
+            const int head = idx / hd, d = idx % hd;
+            v_pool[cache_base + (size_t)head * PE_PAGE * hd + d] = v[idx];
+        }
+    }
+}
+
+extern "C" int pe_rope_store(void* qkv, int dtype, int T, int n_q, int n_kv, int hd, const float* cos_t,
+                             const float* sin_t, const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
+                             const int* block_table, int table_stride, int store, void* stream) {
+    if (T <= 0) return 0;
+    if (hd % 2) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PE_F32)
+        rope_store_kernel<float><<<T, 256, 0, s>>>((float*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
+                                                    (float*)k_pool, (float*)v_pool, block_table, table_stride, store);
+    else if (dtype == PE_BF16)
+        rope_store_kernel<bf16><<<T, 256, 0, s>>>((bf16*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
+                                                   (bf16*)k_pool, (bf16*)v_pool, block_table, table_stride, store);
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}

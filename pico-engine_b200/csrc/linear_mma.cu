@@ -1,0 +1,176 @@
+// out[M, N] = A[M, K] . W[N, K]^T (+ bias) for few rows M (decoding: one row per sequence),
+// bfloat16 operands, float32 accumulation on the tensor cores (mma.sync m16n8k16).
+//
+// With few rows the product is bound by reading W once.  The roles are therefore swapped:
+// 16 rows of W are the M side of the MMA, 8 rows of A (8 sequences) its N side.  A warp owns
+// 16 rows of W and streams them from global memory straight into MMA fragments with 16-byte
+// loads (the k index inside a 32-wide chunk is permuted identically for both operands, which
+// a dot product does not notice); A is small and is read through L1.  No shared memory, no
+// barrier inside the k loop.
+//
+// K is cut into `splits` ranges so that small matrices still fill the GPU; each CTA writes
+// its partial sums to scratch, and the CTA that finishes last for a tile of rows adds the
+// partials in the order of the ranges and applies the epilogue.  `splits` depends on N and
+// K only, so a row's result does not depend on how many rows are beside it.
+//
+// pico-engine leaves decode products to float32 cuBLAS (src/pico_engine/model.py:148-150, 177,
+// 213, 223, 235) or its quantized Triton GEMVs (src/pico_engine/kernels.py:161-344).
+#include "common.cuh"
+
+#define LM_WARPS 4
+#define LM_ROWS (16 * LM_WARPS)        // rows of W per CTA
+#define LM_MAX_M 64
+#define LM_MAX_SPLITS 16
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// epilogue: 0 store float32, 1 store bfloat16, 2 add into float32
+__device__ __forceinline__ void lm_store(void* out, int epilogue, size_t o, float v) {
+    if (epilogue == 0) ((float*)out)[o] = v;
+    else if (epilogue == 1) ((bf16*)out)[o] = __float2bfloat16_rn(v);
+    else ((float*)out)[o] += v;
+}
+
+// NT: number of 8-row tiles of A (M <= 8 * NT)
+template <int NT>
+__global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
+    const bf16* __restrict__ A, const bf16* __restrict__ W, const void* __restrict__ bias, int bias_dtype,
+    void* __restrict__ out, int epilogue, int M, int N, int K, int splits, int k_per_split,
+    float* __restrict__ partial, unsigned int* __restrict__ tickets) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * LM_ROWS + warp * 16;
+    const int split = blockIdx.y;
+    const int k_begin = split * k_per_split;
+    const int k_end = min(K, k_begin + k_per_split);
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+
+    const int r0 = n0 + g, r1 = n0 + g + 8;
+    const bool ok0 = r0 < N, ok1 = r1 < N;
+    const bf16* w0 = W + (size_t)(ok0 ? r0 : 0) * K;
+    const bf16* w1 = W + (size_t)(ok1 ? r1 : 0) * K;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    if (n0 < N) {
+#pragma unroll 4
+        for (int kb = k_begin; kb < k_end; kb += 32) {
+            const int k = kb + t * 8;
+            const bool kin = k < k_end;                      // K and k_per_split are multiples of 8
+            const uint4 wa = (ok0 && kin) ? ldg_stream(w0 + k) : zero;
+            const uint4 wb = (ok1 && kin) ? ldg_stream(w1 + k) : zero;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int m = j * 8 + g;
+                const uint4 a = (m < M && kin) ? __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * K + k)) : zero;
+                mma_bf16(acc[j], wa.x, wb.x, wa.y, wb.y, a.x, a.y);
+                mma_bf16(acc[j], wa.z, wb.z, wa.w, wb.w, a.z, a.w);
+            }
+        }
+    }
+
+    // acc[j][0]: (W row n0+g, A row j*8+2t), [1]: (n0+g, j*8+2t+1), [2]: (n0+g+8, j*8+2t), [3]: (n0+g+8, j*8+2t+1)
+    if (splits == 1) {
+        if (n0 < N) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int n = (e & 2) ? r1 : r0, m = j * 8 + 2 * t + (e & 1);
+                    if (n < N && m < M) {
+                        float v = acc[j][e];
+                        if (bias) v += load_as_f(bias, bias_dtype, n);
+                        lm_store(out, epilogue, (size_t)m * N + n, v);
+                    }
+                }
+        }
+        return;
+    }
+
+    // partial[split][m][n]
+    if (n0 < N) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int n = (e & 2) ? r1 : r0, m = j * 8 + 2 * t + (e & 1);
+                if (n < N && m < M) partial[((size_t)split * M + m) * N + n] = acc[j][e];
+            }
+    }
+    __shared__ unsigned int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(&tickets[blockIdx.x], 1u);
+        s_last = (prev == (unsigned int)splits - 1u) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int rows = min(LM_ROWS, N - blockIdx.x * LM_ROWS);
+    for (int idx = threadIdx.x; idx < rows * M; idx += blockDim.x) {
+        const int m = idx / rows, n = blockIdx.x * LM_ROWS + idx % rows;
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) v += __ldcg(&partial[((size_t)s * M + m) * N + n]);
+        if (bias) v += load_as_f(bias, bias_dtype, n);
+        lm_store(out, epilogue, (size_t)m * N + n, v);
+    }
+    if (threadIdx.x == 0) tickets[blockIdx.x] = 0u;          // ready for the next launch
+}
+
+// The number of K ranges for an [N, K] weight: enough CTAs to occupy the GPU, at least 128
+// columns each.  A function of N and K only.
+extern "C" int pe_linear_mma_splits(int N, int K) {
+    const int tiles = (N + LM_ROWS - 1) / LM_ROWS;
+    int s = 1;
+    while (s < LM_MAX_SPLITS && tiles * s < 2 * 148 && K / (s * 2) >= 128) s *= 2;
+    return s;
+}
+
+extern "C" long long pe_linear_mma_scratch_bytes(int M, int N, int K) {
+    const int s = pe_linear_mma_splits(N, K);
+    return s > 1 ? (long long)s * M * N * 4 : 0;
+}
+
+// `tickets` holds at least ceil(N / 64) zeroed unsigned ints; the kernel leaves them zero.
+extern "C" int pe_linear_mma(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int epilogue,
+                             int M, int N, int K, void* partial, void* tickets, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > LM_MAX_M || K <= 0 || K % 8 || epilogue < 0 || epilogue > 2) return PE_ERR_UNSUPPORTED;
+    if (((uintptr_t)A | (uintptr_t)W) & 15) return PE_ERR_UNSUPPORTED;
+    const int splits = pe_linear_mma_splits(N, K);
+    if (splits > 1 && (!partial || !tickets)) return PE_ERR_UNSUPPORTED;
+    int k_per_split = (K + splits - 1) / splits;
+    k_per_split = (k_per_split + 31) / 32 * 32;
+    dim3 grid((N + LM_ROWS - 1) / LM_ROWS, splits);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = (M + 7) / 8;
+#define LM_GO(NT) linear_mma_kernel<NT><<<grid, 32 * LM_WARPS, 0, s>>>((const bf16*)A, (const bf16*)W, bias, bias_dtype, out, \
+        epilogue, M, N, K, splits, k_per_split, (float*)partial, (unsigned int*)tickets)
+    switch (nt) {
+        case 1: LM_GO(1); break;
+        case 2: LM_GO(2); break;
+        case 3: LM_GO(3); break;
+        case 4: LM_GO(4); break;
+        case 5: LM_GO(5); break;
+        case 6: LM_GO(6); break;
+        case 7: LM_GO(7); break;
+        default: LM_GO(8); break;
+    }
+#undef LM_GO
+    PE_LAUNCH_CHECK();
+    return 0;
+}

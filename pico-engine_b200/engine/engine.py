@@ -1,0 +1,151 @@
+"""The Python entry point: a model folder in, generated token ids out.
+
+In pico-engine's manner (src/pico_engine/engine.py:16-24, 308-337): ``Engine(path)`` loads,
+``Engine.generate(prompt, max_tokens=64, temperature=0.7, top_k=0, top_p=0.9, use_graph=True)``
+generates.  Differences that the scope brings: prompts and results are token ids (there is no
+tokenizer here), ``generate`` also takes a batch of prompts, and draws are seeded.
+"""
+from __future__ import annotations
+
+import os
+from typing import Iterable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import Cache, PAGE
+from ..config.registry import architecture, read_config
+from ..ops.library import core, require_cuda
+from ..sampling import Sampler, SamplingParams
+from ..weights import load_folder, load_into, random_tensor
+from . import generate as loop
+from .graph import GraphedDecode
+from .step import Stepper
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _dtype(d) -> torch.dtype:
+    try:
+        return DTYPES[d]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, not {d!r}") from None
+
+
+class Engine:
+    """A loaded model with its cache, step function and generation loop on one CUDA device.
+
+    ``max_tokens_in_cache``: the most tokens live sequences hold at any time, each rounded up to a
+    page of 64; ``max_context``: the longest single sequence; ``max_batch``: sequences per batch.
+    The cache is allocated on first use and grows when a call needs more.
+    """
+
+    def __init__(self, model_path: Union[str, os.PathLike, None], device: str = "cuda", dtype="bfloat16",
+                 max_tokens_in_cache: Optional[int] = None, max_context: Optional[int] = None, max_batch: int = 64,
+                 _config=None, _seed: Optional[int] = None):
+        self.device = require_cuda(device)
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.dtype = _dtype(dtype)
+        core()                                              # build or load the kernels now, loudly
+        torch.cuda.set_device(self.device)
+        self.config = _config if _config is not None else read_config(os.fspath(model_path))
+        arch = architecture(self.config.ARCHITECTURE)
+        self.model = arch.build_model(self.config, self.dtype, self.device)
+        if _config is None:
+            load_folder(self.model, os.fspath(model_path))
+        else:
+            expected = self.model.expected_tensors()
+            store = torch.bfloat16
+            load_into(self.model, lambda n: random_tensor(n, expected[n], _seed, store, self.device),
+                      {n: s.shape for n, s in expected.items()}, "the random weights")
+        self.max_batch = max_batch
+        self._want_tokens = max_tokens_in_cache
+        self._want_context = max_context
+        self.cache: Optional[Cache] = None
+        self.stepper: Optional[Stepper] = None
+        self._graphs = {}
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, **kwargs) -> "Engine":
+        """An engine with random weights drawn from ``config`` and ``seed`` (bfloat16-rounded
+        values, as the random-weights writer would store them), without a model folder."""
+        return cls(None, _config=config, _seed=seed, **kwargs)
+
+    # ------------------------------------------------------------------ cache
+    def ensure_cache(self, max_tokens: int, max_context: int, max_seqs: Optional[int] = None) -> None:
+        """Make the cache hold ``max_tokens`` tokens (in pages) and sequences of ``max_context``."""
+        max_tokens = max(max_tokens, self._want_tokens or 0, PAGE)
+        max_context = min(max(max_context, self._want_context or 0, 1), self.model.plan.max_positions)
+        max_seqs = max_seqs or max(self.max_batch, 1)
+        c = self.cache
+        if c is not None and c.n_pages * PAGE >= max_tokens and self.stepper.max_context >= max_context \
+                and c.max_seqs >= max_seqs:
+            return
+        if c is not None and c.lengths:
+            raise RuntimeError("the cache cannot grow while sequences are open")
+        self.cache = self.stepper = None
+        self._graphs.clear()
+        self.cache = Cache(self.model.cache_needs(), max_tokens, max_seqs, self.dtype, self.device)
+        self.model.prepare(max_context)
+        self.stepper = Stepper(self.model, self.cache, max_context)
+
+    # ------------------------------------------------------------------ generation
+    @torch.inference_mode()
+    def generate(self, prompt: Union[Sequence[int], Sequence[Sequence[int]]], max_tokens: Union[int, Sequence[int]] = 64,
+                 temperature: float = 0.7, top_k: int = 0, top_p: float = 0.9, use_graph: bool = True,
+                 seed: int = 0, stop_token_ids: Optional[Iterable[int]] = None):
+        """Generated token ids: a list for one prompt (a list of ints), a list of lists for a
+        batch of prompts.  ``stop_token_ids`` defaults to the configuration's eos ids; a stop
+        token ends its sequence and is not returned."""
+        single = len(prompt) > 0 and isinstance(prompt[0], int) or len(prompt) == 0
+        prompts = [list(prompt)] if single else [list(p) for p in prompt]
+        requests = self.generate_requests(prompts, max_tokens, SamplingParams(temperature, top_k, top_p, seed),
+                                          use_graph, stop_token_ids)
+        outs = [r.output for r in requests]
+        return outs[0] if single else outs
+
+    def generate_requests(self, prompts, max_tokens, params: SamplingParams, use_graph: bool = True,
+                          stop_token_ids: Optional[Iterable[int]] = None) -> List[loop.Request]:
+        stop = tuple(self.model.plan.stop_token_ids) if stop_token_ids is None else tuple(stop_token_ids)
+        mnt = [max_tokens] * len(prompts) if isinstance(max_tokens, int) else list(max_tokens)
+        probe = [loop.Request(i, list(p), m) for i, (p, m) in enumerate(zip(prompts, mnt)) if len(p)]
+        if probe:
+            need = [loop.held_tokens(r) for r in probe]
+            budget = self._want_tokens or sum(sorted(need, reverse=True)[:self.max_batch])
+            self.ensure_cache(max(budget, max(need)), max(len(r.prompt) + r.max_new_tokens for r in probe))
+        backend = EngineBackend(self, Sampler(params), use_graph)
+        budget = self.cache.n_pages * PAGE if self.cache is not None else PAGE
+        return loop.generate(backend, prompts, mnt, stop, self.max_batch, budget)
+
+
+class EngineBackend:
+    """The generation loop's backend on the engine's stepper: steps, then chooses on the device
+    and hands the chosen tokens to the host."""
+
+    def __init__(self, engine: Engine, sampler: Sampler, use_graph: bool):
+        self.e, self.sampler, self.use_graph = engine, sampler, use_graph
+
+    def open(self) -> int:
+        return self.e.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.e.cache.close(slot)
+
+    def _int32(self, values) -> torch.Tensor:
+        return torch.tensor(list(values), dtype=torch.int32).to(self.e.device, non_blocking=True)
+
+    def prefill(self, slots, prompts, requests) -> List[int]:
+        logits = self.e.stepper.step(slots, prompts)
+        chosen = self.sampler.choose(logits, self._int32(requests), self._int32([0] * len(slots)))
+        return chosen.tolist()
+
+    def decode(self, slots, tokens, requests, steps) -> List[int]:
+        if self.use_graph:
+            key = (len(slots), self.sampler.params)
+            g = self.e._graphs.get(key)
+            if g is None:
+                g = self.e._graphs[key] = GraphedDecode(self.e.stepper, self.sampler, len(slots))
+            return g.run(slots, tokens, requests, steps).tolist()
+        logits = self.e.stepper.step(slots, [[t] for t in tokens])
+        return self.sampler.choose(logits, self._int32(requests), self._int32(steps)).tolist()

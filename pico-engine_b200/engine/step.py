@@ -1,0 +1,182 @@
+"""The step function: run the given tokens of a batch of sequences, from the cache, as one
+batch, and return the logits at the wanted places.
+
+A step takes sequences that are open in the cache and, for each, the next tokens of that
+sequence (a whole prompt, a piece of one, or one decoded token).  Tokens are packed without
+padding; the cache is read for everything before them.  After the step the sequences are
+longer by what they were given.  pico-engine's counterpart is ``Transformer.forward`` for one
+sequence (src/pico_engine/model.py:129-165), whose prompt must start at position 0
+(model.py:194-197) and which returns the last row only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import Cache, PAGE, pages_for
+from ..parts.base import StepContext
+
+
+class StepError(ValueError):
+    """A step that cannot run: an empty row, a token outside the vocabulary, a sequence that
+    would outgrow the longest one the engine was set up for, a wanted place that is no token
+    of this step."""
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+@dataclass
+class StepLayout:
+    """Where each array of a step lies in the one int32 buffer that is sent to the device."""
+    T: int
+    B: int
+    W: int
+    widths: List[int]
+    ids: int = 0
+    pos: int = 0
+    row: int = 0
+    slots: int = 0
+    want: int = 0
+    tables: Optional[List[int]] = None
+    total: int = 0
+
+    def __post_init__(self):
+        o = 0
+        self.ids = o; o += _pad4(self.T)
+        self.pos = o; o += _pad4(self.T)
+        self.row = o; o += _pad4(self.T)
+        self.slots = o; o += _pad4(self.B)
+        self.want = o; o += _pad4(max(self.W, 1))
+        self.tables = []
+        for w in self.widths:
+            self.tables.append(o); o += _pad4(self.B * w)
+        self.total = o
+
+
+class Stepper:
+    """Owns nothing but scratch: it drives ``model`` over ``cache``."""
+
+    def __init__(self, model, cache: Cache, max_context: int):
+        self.model, self.cache, self.max_context = model, cache, max_context
+        self.device = cache.device
+        self.vocab = model.plan.vocab_size
+        self._ring: List[list] = [[None, None] for _ in range(4)]     # pinned staging buffers and their copy events
+        self._ring_at = 0
+
+    # ------------------------------------------------------------------ building a step
+    def _stage(self, host: np.ndarray):
+        """A pinned buffer holding ``host``.  Buffers are used in turn; one is written again only
+        after the copy that last read it has finished."""
+        slot = self._ring[self._ring_at]
+        self._ring_at = (self._ring_at + 1) % len(self._ring)
+        if slot[1] is not None:
+            slot[1].synchronize()
+        n = host.shape[0]
+        if slot[0] is None or slot[0].numel() < n:
+            slot[0] = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        slot[0].numpy()[:n] = host
+        return slot, slot[0][:n]
+
+    def describe(self, slots: Sequence[int], lens: Sequence[int], want: Optional[Sequence[Sequence[int]]],
+                 token_ids: Optional[Sequence[Sequence[int]]], widths: Optional[List[int]] = None):
+        """Check the step, reserve its pages and lay its arrays out on the host.
+
+        Returns ``(layout, host int32 array, starts)``.  ``want[b]`` are places among row b's
+        tokens of this step; None asks for each row's last token.
+        """
+        cache = self.cache
+        B = len(slots)
+        if B == 0:
+            raise StepError("a step needs at least one sequence")
+        if len(set(slots)) != B:
+            raise StepError("a sequence appears twice in one step")
+        lens = [int(n) for n in lens]
+        starts = [cache.length(s) for s in slots]
+        for b, n in enumerate(lens):
+            if n < 1:
+                raise StepError(f"row {b} brings no token")
+            if starts[b] + n > self.max_context:
+                raise StepError(f"row {b} would reach {starts[b] + n} tokens; the engine was set up for sequences "
+                                f"of at most {self.max_context}")
+        if want is None:
+            want = [[n - 1] for n in lens]
+        T = sum(lens)
+        W = sum(len(w) for w in want)
+        for s, n in zip(slots, lens):
+            cache.reserve(s, n)
+        if widths is None:
+            widths = [max(pages_for(st + n) for st, n in zip(starts, lens))] * len(cache.groups)
+        lay = StepLayout(T, B, W, widths)
+        host = np.zeros(lay.total, dtype=np.int32)
+        cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        for b in range(B):
+            a, e = cu[b], cu[b + 1]
+            host[lay.pos + a: lay.pos + e] = np.arange(starts[b], starts[b] + lens[b], dtype=np.int32)
+            host[lay.row + a: lay.row + e] = b
+            if token_ids is not None:
+                ids = np.asarray(token_ids[b], dtype=np.int64)
+                if ids.shape != (lens[b],):
+                    raise StepError(f"row {b}: {ids.shape[0] if ids.ndim == 1 else ids.shape} tokens given, {lens[b]} announced")
+                if ids.size and (ids.min() < 0 or ids.max() >= self.vocab):
+                    raise StepError(f"row {b} has a token outside the vocabulary of {self.vocab}")
+                host[lay.ids + a: lay.ids + e] = ids
+        host[lay.slots: lay.slots + B] = np.asarray(slots, dtype=np.int32)
+        w_at = lay.want
+        for b, places in enumerate(want):
+            for p in places:
+                if not 0 <= p < lens[b]:
+                    raise StepError(f"row {b}: wanted place {p} is none of its {lens[b]} tokens")
+                host[w_at] = cu[b] + p
+                w_at += 1
+        for g, off in enumerate(lay.tables):
+            host[off: off + B * widths[g]] = cache.page_table(g, slots, widths[g]).reshape(-1)
+        return lay, host, starts
+
+    def context(self, lay: StepLayout, dev: torch.Tensor, lens: List[int], starts: List[int]) -> StepContext:
+        tables = {g: dev[off: off + lay.B * lay.widths[g]].view(lay.B, lay.widths[g])
+                  for g, off in enumerate(lay.tables)}
+        return StepContext(
+            T=lay.T, B=lay.B, dtype=self.model.dtype, device=self.device,
+            tok_pos=dev[lay.pos: lay.pos + lay.T], tok_row=dev[lay.row: lay.row + lay.T],
+            slots=dev[lay.slots: lay.slots + lay.B], lens=list(lens), starts=list(starts),
+            one_token_each=all(n == 1 for n in lens), cache=self.cache, tables=tables,
+            max_context=max(s + n for s, n in zip(starts, lens)))
+
+    def upload(self, host: np.ndarray, dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+        slot, staged = self._stage(host)
+        if dev is None:
+            dev = torch.empty(host.shape[0], dtype=torch.int32, device=self.device)
+        dev[:host.shape[0]].copy_(staged, non_blocking=True)
+        if self.device.type == "cuda":
+            slot[1] = slot[1] or torch.cuda.Event()
+            slot[1].record()
+        return dev
+
+    # ------------------------------------------------------------------ the step
+    @torch.inference_mode()
+    def step(self, slots: Sequence[int], token_ids: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None,
+             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run one step; returns float32 logits [wanted places, vocab] on the device, in the
+        order of the rows and of ``want``.  With ``device_tokens`` (int32 [B], one token per row,
+        already on the device) ``token_ids`` only gives the rows' lengths (all 1)."""
+        if device_tokens is not None:
+            lens = [1] * len(slots)
+            lay, host, starts = self.describe(slots, lens, want, None)
+        else:
+            lens = [len(t) for t in token_ids]
+            lay, host, starts = self.describe(slots, lens, want, token_ids)
+        dev = self.upload(host)
+        ctx = self.context(lay, dev, lens, starts)
+        ids = device_tokens if device_tokens is not None else dev[lay.ids: lay.ids + lay.T]
+        x = self.model.hidden(ids, ctx)
+        for s, n in zip(slots, lens):
+            self.cache.advance(s, n)
+        if lay.W == 0:
+            return torch.empty(0, self.vocab, dtype=torch.float32, device=self.device)
+        return self.model.logits(x, dev[lay.want: lay.want + lay.W])

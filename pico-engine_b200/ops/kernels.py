@@ -1,0 +1,316 @@
+"""One Python function per CUDA kernel: argument checks, then the launch on torch's current
+stream.  Tensors are passed as raw device pointers; outputs are allocated by the caller or
+here with torch's allocator.  There is no other implementation behind these functions.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .library import DTYPE_CODE, KernelError, check, core, stream_ptr
+
+PAGE = 64     # tokens per cache page; PE_PAGE in csrc/common.cuh
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, not {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, not {tuple(t.shape)}")
+
+
+def _code(t: torch.Tensor, name: str) -> int:
+    try:
+        return DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"{name} must be float32 or bfloat16, not {t.dtype}") from None
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows ``ids`` (int32, [T]) of ``table`` [V, H] as float32 [T, H]."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _need(table, "table"); _need(ids, "ids", torch.int32, (T,))
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.float32, device=table.device)
+    _need(out, "out", torch.float32, (T, H))
+    check(core().pe_embed(table.data_ptr(), _code(table, "table"), ids.data_ptr(), out.data_ptr(), T, H, V,
+                          stream_ptr()), "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of float32 rows [T, H]; with ``rows_index`` (int32 [R]) only of those rows."""
+    T, H = x.shape
+    _need(x, "x", torch.float32); _need(weight, "weight", None, (H,))
+    rows = T if rows_index is None else rows_index.shape[0]
+    if rows_index is not None:
+        _need(rows_index, "rows_index", torch.int32)
+    if out is None:
+        out = torch.empty(rows, H, dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype, (rows, H))
+    check(core().pe_rmsnorm(x.data_ptr(), _ptr(rows_index), weight.data_ptr(), _code(weight, "weight"), float(eps),
+                            out.data_ptr(), _code(out, "out"), rows, H, stream_ptr()), "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(gate) * up of [T, 2I] (gate first) as [T, I]."""
+    T, I2 = gate_up.shape
+    _need(gate_up, "gate_up")
+    if I2 % 2:
+        raise KernelError("gate_up needs an even number of columns")
+    if out is None:
+        out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _need(out, "out", gate_up.dtype, (T, I2 // 2))
+    check(core().pe_swiglu(gate_up.data_ptr(), out.data_ptr(), _code(gate_up, "gate_up"), T, I2 // 2, stream_ptr()),
+          "swiglu")
+    return out
+
+
+def residual_add(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x += y in float32; x is the float32 residual stream."""
+    _need(x, "x", torch.float32); _need(y, "y", None, x.shape)
+    check(core().pe_residual_add(x.data_ptr(), y.data_ptr(), _code(y, "y"), x.numel(), stream_ptr()), "residual_add")
+    return x
+
+
+def bias_add(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    M, N = y.shape
+    _need(y, "y"); _need(bias, "bias", None, (N,))
+    check(core().pe_bias_add(y.data_ptr(), _code(y, "y"), bias.data_ptr(), _code(bias, "bias"), M, N, stream_ptr()),
+          "bias_add")
+    return y
+
+
+def rope_store(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, cos: Optional[torch.Tensor],
+               sin: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_row: torch.Tensor,
+               k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+               table_stride: int) -> None:
+    """Rotate the query and key heads of ``qkv`` [T, (n_q + 2 n_kv) * head_dim] in place and
+    write keys and values to the cache pages of their sequences (skipped when ``k_pool`` is None)."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", None, (T, (n_q + 2 * n_kv) * head_dim))
+    _need(tok_pos, "tok_pos", torch.int32); _need(tok_row, "tok_row", torch.int32)
+    if cos is not None:
+        _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32, cos.shape)
+        if cos.shape[1] != head_dim // 2:
+            raise KernelError("cos/sin tables need head_dim/2 columns")
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype, k_pool.shape)
+        _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim):
+            raise KernelError(f"cache pool must be [pages, {n_kv}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
+    check(core().pe_rope_store(qkv.data_ptr(), _code(qkv, "qkv"), T, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin),
+                               tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                               table_stride, 1 if store else 0, stream_ptr()), "rope_store")
+
+
+_EPILOGUE_STORE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M, K] . w [N, K]^T (+ bias) with float32 multiply-adds.  Either stored as
+    ``out_dtype`` or added into the float32 tensor ``accumulate_into`` [M, N]."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a, "a"); _need(w, "w", None, (N, K))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    if accumulate_into is not None:
+        _need(accumulate_into, "accumulate_into", torch.float32, (M, N))
+        out, epilogue = accumulate_into, 2
+    else:
+        if out is None:
+            out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+        _need(out, "out", None, (M, N))
+        epilogue = _EPILOGUE_STORE[out.dtype]
+    check(core().pe_linear_simt(a.data_ptr(), _code(a, "a"), w.data_ptr(), _code(w, "w"), _ptr(bias),
+                                0 if bias is None else _code(bias, "bias"), out.data_ptr(), epilogue, M, N, K,
+                                stream_ptr()), "linear_simt")
+    return out
+
+
+def attention_generic(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
+                      tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of T tokens over the cache.  ``q`` holds the query heads of token t at
+    ``t * q_stride + h * head_dim``; the result is [T, n_heads * head_dim] in q's dtype."""
+    T = tok_pos.shape[0]
+    _need(q, "q"); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype, k_pool.shape)
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pool must be [pages, {n_kv_heads}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
+    _need(block_table, "block_table", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32, (T,)); _need(tok_row, "tok_row", torch.int32, (T,))
+    if out is None:
+        out = torch.empty(T, n_heads * head_dim, dtype=q.dtype, device=q.device)
+    _need(out, "out", q.dtype, (T, n_heads * head_dim))
+    check(core().pe_attention_generic(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                      _code(q, "q"), block_table.data_ptr(), table_stride, tok_pos.data_ptr(),
+                                      tok_row.data_ptr(), T, n_heads, n_kv_heads, head_dim, window or 0, float(scale),
+                                      stream_ptr()), "attention_generic")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    B, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, (B,))
+    check(core().pe_argmax(logits.data_ptr(), out.data_ptr(), B, V, stream_ptr()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, request: torch.Tensor,
+           step: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One draw per row of float32 logits [B, V]; row b uses the uniform of (seed, request[b], step[b])."""
+    B, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(request, "request", torch.int32, (B,)); _need(step, "step", torch.int32, (B,))
+    if not temperature > 0:
+        raise KernelError("sample needs a positive temperature; use argmax for greedy choice")
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, (B,))
+    check(core().pe_sample(logits.data_ptr(), out.data_ptr(), B, V, float(temperature), int(top_k), float(top_p),
+                           int(seed) & ((1 << 64) - 1), request.data_ptr(), step.data_ptr(), stream_ptr()), "sample")
+    return out
+
+
+def draw_uniform(seed: int, request: int, step: int) -> float:
+    """The uniform the sampling kernel uses for (seed, request, step), computed on the host."""
+    m = (1 << 64) - 1
+    return float(core().pe_draw_uniform(seed & m, request & m, step & m))
+
+
+# ---------------------------------------------------------------------------- tensor-core kernels (bfloat16)
+
+def linear_mma_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel takes these operands (else another one is used)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= 64 and a.shape[1] % 8 == 0
+            and a.is_contiguous() and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_mma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M <= 64, K] . w [N, K]^T (+ bias), bfloat16 operands, float32 accumulation on the
+    tensor cores; stored as ``out_dtype`` or added into float32 ``accumulate_into``."""
+    from .workspace import scratch
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a, "a", torch.bfloat16); _need(w, "w", torch.bfloat16, (N, K))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    if accumulate_into is not None:
+        _need(accumulate_into, "accumulate_into", torch.float32, (M, N))
+        out, epilogue = accumulate_into, 2
+    else:
+        if out is None:
+            out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+        _need(out, "out", None, (M, N))
+        epilogue = _EPILOGUE_STORE[out.dtype]
+    lib = core()
+    partial = tickets = None
+    if lib.pe_linear_mma_splits(N, K) > 1:
+        partial = scratch("linear_mma.partial", lib.pe_linear_mma_scratch_bytes(64, N, K), a.device).data_ptr()
+        tickets = scratch("linear_mma.tickets", 4 * ((N + 63) // 64), a.device, zeroed=True).data_ptr()
+    check(lib.pe_linear_mma(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
+                            out.data_ptr(), epilogue, M, N, K, partial, tickets, stream_ptr()), "linear_mma")
+    return out
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                     k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
+                     tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
+                     max_context: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of T single tokens (bfloat16) over the cache; ``max_context`` bounds every
+    token's position + 1 and fixes the launch shape."""
+    from .library import for_head_dim
+    from .workspace import scratch
+    T = tok_pos.shape[0]
+    _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pool must be [pages, {n_kv_heads}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
+    _need(block_table, "block_table", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32, (T,)); _need(tok_row, "tok_row", torch.int32, (T,))
+    if out is None:
+        out = torch.empty(T, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
+    _need(out, "out", torch.bfloat16, (T, n_heads * head_dim))
+    lib = for_head_dim(head_dim)
+    nbytes = lib.pe_attention_decode_scratch_bytes(T, n_heads, n_kv_heads, max_context)
+    ws = scratch("attention_decode.partial", nbytes, q.device).data_ptr() if nbytes else None
+    check(lib.pe_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                  block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
+                                  n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context), ws,
+                                  stream_ptr()), "attention_decode")
+    return out
+
+
+PREFILL_TILE = 64
+
+
+def prefill_tiles(lens, starts, device) -> torch.Tensor:
+    """int32 [tiles, 4] = (batch row, first packed token, tokens, position of the first token):
+    the packed tokens of a step cut into runs of at most 64 tokens of one sequence."""
+    rows = []
+    tok = 0
+    for b, (n, st) in enumerate(zip(lens, starts)):
+        for off in range(0, n, PREFILL_TILE):
+            rows.append((b, tok + off, min(PREFILL_TILE, n - off), st + off))
+        tok += n
+    return torch.tensor(rows, dtype=torch.int32).to(device, non_blocking=True)
+
+
+def attention_prefill(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
+                      tiles: torch.Tensor, n_tokens: int, window: Optional[int], scale: float,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention (bfloat16) of the token runs ``tiles`` over the cache."""
+    from .library import for_head_dim
+    _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pool must be [pages, {n_kv_heads}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
+    _need(block_table, "block_table", torch.int32); _need(tiles, "tiles", torch.int32)
+    if out is None:
+        out = torch.empty(n_tokens, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
+    _need(out, "out", torch.bfloat16, (n_tokens, n_heads * head_dim))
+    check(for_head_dim(head_dim).pe_attention_prefill(
+        q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+        table_stride, tiles.data_ptr(), None, None, tiles.shape[0], n_heads, n_kv_heads, head_dim, window or 0,
+        float(scale), stream_ptr()), "attention_prefill")
+    return out
+
+
+def attention(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int, k_pool: torch.Tensor,
+              v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int, tok_pos: torch.Tensor,
+              tok_row: torch.Tensor, window: Optional[int], scale: float, ctx) -> torch.Tensor:
+    """Attention of the step's tokens over the cache, with the kernel the step calls for:
+    bfloat16 uses the tensor-core kernels (single tokens: decode; longer runs: prefill),
+    float32 the float32 kernel."""
+    if q.dtype == torch.bfloat16:
+        if ctx.one_token_each:
+            return attention_decode(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table,
+                                    table_stride, tok_pos, tok_row, window, scale, ctx.max_context)
+        tiles = ctx.scratch.get("prefill_tiles")
+        if tiles is None:
+            tiles = ctx.scratch["prefill_tiles"] = prefill_tiles(ctx.lens, ctx.starts, q.device)
+        return attention_prefill(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table,
+                                 table_stride, tiles, tok_pos.shape[0], window, scale)
+    return attention_generic(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, table_stride,
+                             tok_pos, tok_row, window, scale)

@@ -1,0 +1,37 @@
+"""out = a . w^T (+ bias), stored or added into the float32 residual stream: the choice of
+kernel for a matrix product.
+
+* bfloat16 activations and weights, few rows (decoding): the tensor-core weight-streaming
+  kernel of ``csrc/linear_mma.cu`` with bias and residual in its epilogue.
+* bfloat16, many rows (prompts): the library product (cuBLAS through ``torch.mm``), which is
+  where pico-engine uses a library too (src/pico_engine/model.py:177, 213, 223, 235), followed
+  by this library's bias or residual kernel.
+* anything else (the float32 engine; weights that were stored in float32): float32
+  multiply-adds on the CUDA cores, ``csrc/linear_simt.cu``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import kernels
+
+SMALL_M = 64        # up to this many rows the weight-streaming kernel is used
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        M = a.shape[0]
+        if M <= SMALL_M and kernels.linear_mma_takes(a, w):
+            return kernels.linear_mma(a, w, bias, out_dtype, accumulate_into)
+        y = torch.mm(a, w.t())
+        if accumulate_into is not None:
+            if bias is not None:
+                kernels.bias_add(y, bias)
+            return kernels.residual_add(accumulate_into, y)
+        if bias is not None:
+            kernels.bias_add(y, bias)
+        return y if (out_dtype or a.dtype) == y.dtype else y.to(out_dtype)
+    return kernels.linear_simt(a, w, bias, out_dtype, accumulate_into)

@@ -1,0 +1,164 @@
+"""Interfaces of the parts of a layer, the context a step hands them, and the registries that
+map a part's description (``config.specs``) to its implementation.
+
+No part knows which model it is in: it gets its sizes and constants from its spec, its
+tensors by the names in its spec, and everything about the running step from the
+:class:`StepContext`.
+
+Interfaces
+----------
+Norm          ``forward(x_f32 [T,H], out_dtype, rows_index=None) -> [rows,H]``
+Position      ``prepare(max_positions)``; ``rotate_and_store(qkv, n_q, n_kv, head_dim, ctx, kv)``
+Mixer         ``cache_needs()``; ``prepare(max_positions)``; ``apply(h, ctx, entry, cache_entry,
+              owns_cache) -> y``; optionally ``add_to(x, norm, ctx, ...)`` fused
+FeedForward   ``apply(h, ctx) -> y``; optionally ``add_to(x, norm, ctx)`` fused
+Arrangement   ``run(layer, x, ctx, entry, cache_entry, owns_cache)``: updates ``x`` in place
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..cache import CacheNeeds
+from ..config.specs import ConfigError, PartSpec
+from ..weights.loader import ParamSpec
+
+
+@dataclass
+class KVView:
+    """Keys and values of one schedule entry for the running step."""
+    k: torch.Tensor               # [page, kv head, PAGE, head_dim]
+    v: torch.Tensor
+    table: torch.Tensor           # int32 [B, stride]: physical page of each logical page of each batch row
+    stride: int
+    window: Optional[int]
+
+
+@dataclass
+class StepContext:
+    """Everything a part may know about the running step.
+
+    The step runs ``T`` tokens of ``B`` sequences, packed sequence after sequence.  Token t
+    belongs to batch row ``tok_row[t]`` and stands at position ``tok_pos[t]`` of its sequence.
+    """
+    T: int
+    B: int
+    dtype: torch.dtype                    # dtype of activations and cache
+    device: torch.device
+    tok_pos: torch.Tensor                 # int32 [T], device
+    tok_row: torch.Tensor                 # int32 [T], device
+    slots: torch.Tensor                   # int32 [B], device: sequence slot of each batch row
+    lens: List[int]                       # tokens of each row in this step (host)
+    starts: List[int]                     # position of each row's first token (host)
+    one_token_each: bool                  # every row brings exactly one token
+    cache: object                         # cache.Cache
+    tables: Dict[int, torch.Tensor] = field(default_factory=dict)    # group -> int32 [B, stride]
+    max_context: int = 0                  # upper bound of any row's length after the step
+    scratch: Dict[str, torch.Tensor] = field(default_factory=dict)   # named buffers that live as long as the step
+
+    def kv(self, cache_entry: int) -> KVView:
+        g = self.cache.group_of[cache_entry]
+        k, v = self.cache.pools(cache_entry)
+        t = self.tables[g]
+        return KVView(k, v, t, t.shape[1], self.cache.groups[g].need.window)
+
+    def state(self, cache_entry: int) -> Optional[torch.Tensor]:
+        """[slot, elems] float32; row ``slots[b]`` is batch row b's state."""
+        return self.cache.state_of(cache_entry)
+
+
+class Part:
+    def __init__(self, spec: PartSpec, dtype: torch.dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+
+    def expected_tensors(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def take_tensors(self, get: Callable[[str], torch.Tensor]) -> None:
+        pass
+
+    def prepare(self, max_positions: int) -> None:
+        """Called once before the first step, with the longest sequence the cache can hold."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Position(Part):
+    def rotate_and_store(self, qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, ctx: StepContext,
+                         kv: Optional[KVView]) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds()
+
+    def apply(self, h: torch.Tensor, ctx: StepContext, entry: int, cache_entry: int, owns_cache: bool) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_to(self, x: torch.Tensor, norm: Norm, ctx: StepContext, entry: int, cache_entry: int, owns_cache: bool) -> None:
+        """x += apply(norm(x)); parts override this to fuse the norm and the residual sum."""
+        from ..ops import kernels
+        kernels.residual_add(x, self.apply(norm.forward(x, ctx.dtype), ctx, entry, cache_entry, owns_cache).contiguous())
+
+
+class FeedForward(Part):
+    def apply(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_to(self, x: torch.Tensor, norm: Norm, ctx: StepContext) -> None:
+        from ..ops import kernels
+        kernels.residual_add(x, self.apply(norm.forward(x, ctx.dtype), ctx).contiguous())
+
+
+# ------------------------------------------------------------------ registries
+
+NORMS: Dict[type, type] = {}
+POSITIONS: Dict[type, type] = {}
+MIXERS: Dict[type, type] = {}
+FEED_FORWARDS: Dict[type, type] = {}
+ARRANGEMENTS: Dict[str, Callable] = {}
+
+
+def _register(table: Dict[type, type], spec_class: type):
+    def deco(cls):
+        table[spec_class] = cls
+        return cls
+    return deco
+
+
+def register_norm(spec_class: type):
+    return _register(NORMS, spec_class)
+
+
+def register_position(spec_class: type):
+    return _register(POSITIONS, spec_class)
+
+
+def register_mixer(spec_class: type):
+    return _register(MIXERS, spec_class)
+
+
+def register_feed_forward(spec_class: type):
+    return _register(FEED_FORWARDS, spec_class)
+
+
+def register_arrangement(name: str):
+    def deco(fn):
+        ARRANGEMENTS[name] = fn
+        return fn
+    return deco
+
+
+def build_part(table: Dict[type, type], kind: str, spec: PartSpec, dtype, device) -> Part:
+    try:
+        cls = table[type(spec)]
+    except KeyError:
+        known = ", ".join(sorted(c.__name__ for c in table)) or "none"
+        raise ConfigError(f"no {kind} is registered for {type(spec).__name__}; registered: {known}") from None
+    return cls(spec, dtype, device)
