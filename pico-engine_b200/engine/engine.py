@@ -17,7 +17,7 @@ from ..config.registry import architecture, read_config
 from ..ops.library import core, require_cuda
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_folder, load_into, random_tensor
-from . import generate as loop
+from .generate import Request, generate as run_generation, held_tokens
 from .graph import GraphedDecode
 from .step import Stepper
 
@@ -42,7 +42,7 @@ class Engine:
 
     def __init__(self, model_path: Union[str, os.PathLike, None], device: str = "cuda", dtype="bfloat16",
                  max_tokens_in_cache: Optional[int] = None, max_context: Optional[int] = None, max_batch: int = 64,
-                 _config=None, _seed: Optional[int] = None):
+                 _config=None, _seed: Optional[int] = None, _draw_on="cpu"):
         self.device = require_cuda(device)
         if self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
@@ -57,7 +57,7 @@ class Engine:
         else:
             expected = self.model.expected_tensors()
             store = torch.bfloat16
-            load_into(self.model, lambda n: random_tensor(n, expected[n], _seed, store, self.device),
+            load_into(self.model, lambda n: random_tensor(n, expected[n], _seed, store, _draw_on),
                       {n: s.shape for n, s in expected.items()}, "the random weights")
         self.max_batch = max_batch
         self._want_tokens = max_tokens_in_cache
@@ -67,10 +67,11 @@ class Engine:
         self._graphs = {}
 
     @classmethod
-    def from_config(cls, config, seed: int = 0, **kwargs) -> "Engine":
-        """An engine with random weights drawn from ``config`` and ``seed`` (bfloat16-rounded
-        values, as the random-weights writer would store them), without a model folder."""
-        return cls(None, _config=config, _seed=seed, **kwargs)
+    def from_config(cls, config, seed: int = 0, draw_on="cpu", **kwargs) -> "Engine":
+        """An engine with random weights drawn from ``config`` and ``seed``, without a model
+        folder: the values the random-weights writer would store in bfloat16.  ``draw_on`` "cuda"
+        draws on the device, which is quicker for large models and gives other values."""
+        return cls(None, _config=config, _seed=seed, _draw_on=draw_on, **kwargs)
 
     # ------------------------------------------------------------------ cache
     def ensure_cache(self, max_tokens: int, max_context: int, max_seqs: Optional[int] = None) -> None:
@@ -106,17 +107,17 @@ class Engine:
         return outs[0] if single else outs
 
     def generate_requests(self, prompts, max_tokens, params: SamplingParams, use_graph: bool = True,
-                          stop_token_ids: Optional[Iterable[int]] = None) -> List[loop.Request]:
+                          stop_token_ids: Optional[Iterable[int]] = None) -> List[Request]:
         stop = tuple(self.model.plan.stop_token_ids) if stop_token_ids is None else tuple(stop_token_ids)
         mnt = [max_tokens] * len(prompts) if isinstance(max_tokens, int) else list(max_tokens)
-        probe = [loop.Request(i, list(p), m) for i, (p, m) in enumerate(zip(prompts, mnt)) if len(p)]
+        probe = [Request(i, list(p), m) for i, (p, m) in enumerate(zip(prompts, mnt)) if len(p)]
         if probe:
-            need = [loop.held_tokens(r) for r in probe]
+            need = [held_tokens(r) for r in probe]
             budget = self._want_tokens or sum(sorted(need, reverse=True)[:self.max_batch])
             self.ensure_cache(max(budget, max(need)), max(len(r.prompt) + r.max_new_tokens for r in probe))
         backend = EngineBackend(self, Sampler(params), use_graph)
         budget = self.cache.n_pages * PAGE if self.cache is not None else PAGE
-        return loop.generate(backend, prompts, mnt, stop, self.max_batch, budget)
+        return run_generation(backend, prompts, mnt, stop, self.max_batch, budget)
 
 
 class EngineBackend:

@@ -43,12 +43,12 @@ class GraphedDecode:
         pad = (B + 3) & ~3
         self.host[self.extra: self.extra + B] = np.asarray(requests, dtype=np.int32)
         self.host[self.extra + pad: self.extra + pad + B] = np.asarray(steps, dtype=np.int32)
-        self._starts = starts
+        self._starts, self._slots = starts, list(slots)
 
     def _forward(self) -> None:
         lay, B = self.layout, self.B
         pad = (B + 3) & ~3
-        ctx = self.stepper.context(lay, self.dev, [1] * B, [0] * B)
+        ctx = self.stepper.context(lay, self.dev, [1] * B, [0] * B, self._slots)
         ctx.max_context = self.stepper.max_context       # launch shapes must not depend on the step
         ctx.starts = [self.stepper.max_context - 1] * B
         ids = self.dev[lay.ids: lay.ids + B]

@@ -137,13 +137,14 @@ class Stepper:
             host[off: off + B * widths[g]] = cache.page_table(g, slots, widths[g]).reshape(-1)
         return lay, host, starts
 
-    def context(self, lay: StepLayout, dev: torch.Tensor, lens: List[int], starts: List[int]) -> StepContext:
+    def context(self, lay: StepLayout, dev: torch.Tensor, lens: List[int], starts: List[int],
+                slot_ids: Sequence[int] = ()) -> StepContext:
         tables = {g: dev[off: off + lay.B * lay.widths[g]].view(lay.B, lay.widths[g])
                   for g, off in enumerate(lay.tables)}
         return StepContext(
             T=lay.T, B=lay.B, dtype=self.model.dtype, device=self.device,
             tok_pos=dev[lay.pos: lay.pos + lay.T], tok_row=dev[lay.row: lay.row + lay.T],
-            slots=dev[lay.slots: lay.slots + lay.B], lens=list(lens), starts=list(starts),
+            slots=dev[lay.slots: lay.slots + lay.B], slot_ids=list(slot_ids), lens=list(lens), starts=list(starts),
             one_token_each=all(n == 1 for n in lens), cache=self.cache, tables=tables,
             max_context=max(s + n for s, n in zip(starts, lens)))
 
@@ -172,7 +173,7 @@ class Stepper:
             lens = [len(t) for t in token_ids]
             lay, host, starts = self.describe(slots, lens, want, token_ids)
         dev = self.upload(host)
-        ctx = self.context(lay, dev, lens, starts)
+        ctx = self.context(lay, dev, lens, starts, slots)
         ids = device_tokens if device_tokens is not None else dev[lay.ids: lay.ids + lay.T]
         x = self.model.hidden(ids, ctx)
         for s, n in zip(slots, lens):

@@ -50,6 +50,7 @@ class StepContext:
     tok_pos: torch.Tensor                 # int32 [T], device
     tok_row: torch.Tensor                 # int32 [T], device
     slots: torch.Tensor                   # int32 [B], device: sequence slot of each batch row
+    slot_ids: List[int]                   # the same on the host
     lens: List[int]                       # tokens of each row in this step (host)
     starts: List[int]                     # position of each row's first token (host)
     one_token_each: bool                  # every row brings exactly one token

@@ -1,0 +1,232 @@
+"""The engine against the plain implementation: every way of cutting the same requests into
+steps, in float32 and in bfloat16, on both tiny configurations."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import replay
+from conftest import TINY, close_enough, make_weights, write_model
+
+pytestmark = pytest.mark.gpu
+
+SEEDS = {"A": 0, "B": 1}
+
+
+def random_requests(cfg, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return {f"r{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """{(config, dtype): (engine, cfg, weights)}; the folders live in a temporary place."""
+    from pico_engine.engine.engine import Engine
+    root = tmp_path_factory.mktemp("models")
+    out = {}
+    for name, cfg in TINY.items():
+        weights = make_weights(cfg, SEEDS[name], sharp=True)
+        folder = write_model(root / name, cfg, weights)
+        for dtype in ("float32", "bfloat16"):
+            out[(name, dtype)] = (Engine(folder, dtype=dtype), dict(cfg), weights)
+    return out
+
+
+LENGTHS = {"A": [5, 9, 13, 40, 66, 100, 33, 1], "B": [1, 17, 40, 64, 65, 130, 200, 35]}
+CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_requests(models, name, dtype):
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, LENGTHS[name], 10)
+    replay.compare(replay.run_in_process(eng, replay.whole(reqs)), replay.plain_logits(cfg, w, reqs), dtype, "whole")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(models, name, dtype):
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, LENGTHS[name], 11)
+    replay.compare(replay.run_in_process(eng, replay.tail(reqs, 32)), replay.plain_logits(cfg, w, reqs), dtype, "tail")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("batch_size,fraction", [(3, 0.5), (4, 0.2), (8, 0.9)])
+def test_unequal_batches_one_after_another(models, name, dtype, batch_size, fraction):
+    """Shorter requests end earlier; the next batch takes the slots and pages just given back
+    (the cache is sized for one batch only)."""
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, LENGTHS[name] + LENGTHS[name][::-1], 12 + batch_size)
+    steps = replay.batched(reqs, batch_size, fraction)
+    assert replay.max_tokens_of(steps) < sum((len(t) + 63) // 64 * 64 for t in reqs.values())
+    replay.compare(replay.run_in_process(eng, steps), replay.plain_logits(cfg, w, reqs), dtype, "batched")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_cutting_does_not_change_float32_results_beyond_rounding(models, name, dtype):
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, LENGTHS[name], 13)
+    a = replay.run_in_process(eng, replay.whole(reqs))
+    b = replay.run_in_process(eng, replay.tail(reqs, 32))
+    c = replay.run_in_process(eng, replay.batched(reqs, 3, 0.5))
+    for key in a:
+        for other in (b, c):
+            ok, msg = close_enough(torch.from_numpy(other[key]), torch.from_numpy(a[key]), dtype)
+            assert ok, (key, msg)
+            if dtype == "float32":
+                assert float(np.abs(other[key] - a[key]).max()) <= 2e-5 * max(1.0, float(np.abs(a[key]).max())), key
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_long_decoding_and_first_tokens(models, name, dtype):
+    """Three prompt tokens, then token by token up to the longest sequence the model allows:
+    crosses cache pages and, for tiny-B, leaves the window's pages behind."""
+    eng, cfg, w = models[(name, dtype)]
+    n = cfg["max_position_embeddings"]
+    reqs = random_requests(cfg, [n, 2, 3], 14)
+    steps = replay.tail(reqs, n - 3)
+    got = replay.run_in_process(eng, steps)
+    replay.compare(got, replay.plain_logits(cfg, w, reqs), dtype, "long decode")
+    if name == "B":                                     # in steady state the window group held about a window
+        eng.ensure_cache(512, 256, max_seqs=8)
+        s = eng.cache.open()
+        eng.stepper.step([s], [reqs["r0"][:100]])
+        for t in reqs["r0"][100:240]:
+            eng.stepper.step([s], [[t]])
+        held = [sum(p >= 0 for p in g.table[s]) for g in eng.cache.groups]
+        assert held == [4, 1] or held == [4, 2], held
+        eng.cache.close(s)
+
+
+def test_padding_and_neighbours_change_nothing(models):
+    """A request's float32 logits with and without neighbours in the batch."""
+    eng, cfg, w = models[("B", "float32")]
+    reqs = random_requests(cfg, [50, 7, 120], 15)
+    alone = replay.run_in_process(eng, replay.whole({"r0": reqs["r0"]}))
+    together = replay.run_in_process(eng, [{"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}
+                                                                    for r, t in reqs.items()], "end": list(reqs)}])
+    for p in range(50):
+        assert np.array_equal(alone[("r0", p)], together[("r0", p)]), p
+
+
+def test_step_refuses_what_it_cannot_run(models):
+    from pico_engine.cache import CacheFull
+    from pico_engine.engine.step import StepError
+    eng, cfg, w = models[("A", "float32")]
+    eng.cache = eng.stepper = None
+    eng.ensure_cache(128, 128, max_seqs=2)
+    s = eng.cache.open()
+    for bad, err in ((([s], [[]]), StepError), (([s], [[999]]), StepError), (([s, s], [[1], [2]]), StepError),
+                     (([s], [[1, 2]], [[5]]), StepError), (([s], [list(range(129))]), StepError)):
+        with pytest.raises(err):
+            eng.stepper.step(*bad)
+    t = eng.cache.open()
+    eng.stepper.step([s], [[1] * 100])
+    with pytest.raises(CacheFull):
+        eng.stepper.step([t], [[1] * 100])
+    eng.cache.close(s); eng.cache.close(t)
+
+
+# ---------------------------------------------------------------------------- generation through the entry point
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_greedy_generation_float32(models, name, use_graph):
+    eng, cfg, w = models[(name, "float32")]
+    lengths = [5, 9, 13] if name == "A" else [1, 17, 40, 64]
+    prompts = list(random_requests(cfg, lengths, 16).values())
+    got = eng.generate(prompts, max_tokens=8 if name == "A" else 16, temperature=0.0, use_graph=use_graph)
+    want = [plain.generate(cfg, w, p, 8 if name == "A" else 16) for p in prompts]
+    assert got == want
+    assert eng.generate(prompts[0], max_tokens=4, temperature=0) == want[0][:4]      # one prompt in, one list out
+    assert not eng.cache.lengths
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_seeded_sampling_float32(models, name):
+    eng, cfg, w = models[(name, "float32")]
+    prompts = list(random_requests(cfg, [1, 17, 40, 64], 17).values())
+    kw = dict(temperature=0.8, top_k=0, top_p=1.0, seed=5)
+    got = eng.generate(prompts, max_tokens=16, **kw)
+    want = [plain.generate(cfg, w, p, 16, request=i, **kw) for i, p in enumerate(prompts)]
+    assert got == want
+    again = eng.generate(prompts[::-1], max_tokens=16, **kw)
+    assert again != got[::-1]                                     # a request's stream is named by its place in the call
+    assert eng.generate(prompts, max_tokens=16, **kw) == got
+    narrowed = eng.generate(prompts, max_tokens=16, temperature=0.8, top_k=3, top_p=0.7, seed=5, use_graph=False)
+    assert narrowed == [plain.generate(cfg, w, p, 16, temperature=0.8, top_k=3, top_p=0.7, seed=5, request=i)
+                        for i, p in enumerate(prompts)]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_stop_tokens_and_many_batches(models, name):
+    eng, cfg, w = models[(name, "float32")]
+    prompts = list(random_requests(cfg, [3, 30, 8, 21, 2, 14, 9], 18).values())
+    free = [plain.generate(cfg, w, p, 12) for p in prompts]
+    stop = (free[1][4], free[3][0])
+    eng.max_batch, old = 3, eng.max_batch
+    try:
+        got = eng.generate(prompts, max_tokens=12, temperature=0.0, stop_token_ids=stop)
+    finally:
+        eng.max_batch = old
+    want = [plain.generate(cfg, w, p, 12, stop=stop) for p in prompts]
+    assert got == want and len(got[1]) <= 4 and got[3] == []
+    assert not eng.cache.lengths and eng.cache.slots.free_count == eng.cache.max_seqs
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_greedy_generation_bfloat16(models, name, use_graph):
+    """Each chosen token must be a (near) maximum of the plain logits for the engine's own
+    prefix: bfloat16 rounding may swap candidates whose plain logits are within the tolerance."""
+    eng, cfg, w = models[(name, "bfloat16")]
+    prompts = list(random_requests(cfg, [5, 9, 13, 40], 19).values())
+    got = eng.generate(prompts, max_tokens=12, temperature=0.0, use_graph=use_graph)
+    exact = 0
+    for p, out in zip(prompts, got):
+        assert len(out) == 12
+        logits = plain.forward(cfg, w, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max())), (i, tok)
+            exact += int(row.argmax()) == tok
+    assert exact >= 40
+
+
+def test_graph_and_eager_decode_agree(models):
+    eng, cfg, w = models[("B", "bfloat16")]
+    prompts = list(random_requests(cfg, [20, 70, 3], 20).values())
+    a = eng.generate(prompts, max_tokens=70, temperature=0.7, top_p=0.9, seed=3, use_graph=True)
+    b = eng.generate(prompts, max_tokens=70, temperature=0.7, top_p=0.9, seed=3, use_graph=False)
+    assert a == b
+
+
+def test_weights_stored_in_float32_stay_so(tmp_path):
+    """A checkpoint whose norms and one projection are stored in 32 bits, run by the bfloat16 engine."""
+    from pico_engine.engine.engine import Engine
+    cfg = dict(TINY["A"])
+    w = make_weights(cfg, 3, sharp=True)
+    f32 = {n for n in w if "norm" in n} | {"model.layers.1.mlp.down_proj.weight"}
+    eng = Engine(write_model(tmp_path / "m", cfg, w, float32_names=f32), dtype="bfloat16")
+    assert eng.model.layers[1].feed_forward.w_down.dtype == torch.float32
+    reqs = random_requests(cfg, [40, 9], 21)
+    replay.compare(replay.run_in_process(eng, replay.tail(reqs, 8)), replay.plain_logits(cfg, w, reqs), "bfloat16", "mixed")
+
+
+def test_random_weights_mode_end_to_end(tmp_path):
+    """The library's own writer, its loader, and generation; compared with the plain implementation
+    reading the same folder through the safetensors package."""
+    from safetensors.torch import load_file
+    from pico_engine.config import config_from_dict
+    from pico_engine.engine.engine import Engine
+    from pico_engine.weights import write_random_model
+    cfg = dict(TINY["B"])
+    write_random_model(config_from_dict(cfg), 1, str(tmp_path / "r"))
+    w = {k: v.float() for k, v in load_file(str(tmp_path / "r" / "model.safetensors")).items()}
+    eng = Engine(str(tmp_path / "r"), dtype="float32")
+    reqs = random_requests(cfg, [1, 17, 40, 64], 22)
+    replay.compare(replay.run_in_process(eng, replay.batched(reqs, 4, 1.0)), replay.plain_logits(cfg, w, reqs), "float32", "random")
+    direct = Engine.from_config(config_from_dict(cfg), seed=1, dtype="float32")
+    assert torch.equal(direct.model.head.cpu(), w["lm_head.weight"])

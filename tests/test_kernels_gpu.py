@@ -1,0 +1,366 @@
+"""Each CUDA kernel alone against the plain float32 formulas, at sizes other than the engine's."""
+import math
+import random
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f32": torch.float32, "bf16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from pico_engine.ops import kernels
+    return kernels
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def bf(t):
+    """Values rounded to bfloat16, kept in float32."""
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+# ---------------------------------------------------------------------------- small kernels
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_embed(K, dtype):
+    table = bf(rnd(1000, 200))
+    ids = torch.tensor([0, 999, 5, 5, 321], dtype=torch.int32)
+    out = K.embed(dev(table.to(DT[dtype])), dev(ids))
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), table[ids.long()])
+
+
+@pytest.mark.parametrize("H", [100, 896, 3584])
+@pytest.mark.parametrize("wdtype,odtype", [("f32", "f32"), ("bf16", "bf16"), ("f32", "bf16")])
+def test_rmsnorm(K, H, wdtype, odtype):
+    x, w = rnd(7, H, seed=1, scale=3.0), bf(1 + rnd(H, seed=2) * 0.1)
+    want = plain.rms_norm(x, w, 1e-5)
+    got = K.rmsnorm(dev(x), dev(w.to(DT[wdtype])), 1e-5, DT[odtype])
+    tol = 1e-5 if odtype == "f32" else 2e-2
+    assert got.dtype == DT[odtype] and torch.allclose(got.float().cpu(), want, atol=tol, rtol=tol)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    got = K.rmsnorm(dev(x), dev(w.to(DT[wdtype])), 1e-5, DT[odtype], dev(rows))
+    assert torch.allclose(got.float().cpu(), want[rows.long()], atol=tol, rtol=tol)
+
+
+def test_rmsnorm_eps_matters(K):
+    x, w = torch.full((1, 64), 1e-3), torch.ones(64)
+    for eps in (1e-6, 1e-2):
+        got = K.rmsnorm(dev(x), dev(w), eps, torch.float32).cpu()
+        assert torch.allclose(got, plain.rms_norm(x, w, eps), rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_swiglu(K, dtype):
+    gu = bf(rnd(5, 2 * 352, seed=3, scale=2.0))
+    want = plain.swiglu(gu[:, :352], gu[:, 352:])
+    got = K.swiglu(dev(gu.to(DT[dtype])))
+    assert torch.allclose(got.float().cpu(), want, atol=1e-5 if dtype == "f32" else 3e-2, rtol=1e-5 if dtype == "f32" else 1e-2)
+
+
+def test_residual_and_bias_add(K):
+    x, y, b = rnd(6, 50, seed=1), bf(rnd(6, 50, seed=2)), rnd(50, seed=3)
+    got = K.residual_add(dev(x.clone()), dev(y.to(torch.bfloat16)))
+    assert torch.allclose(got.cpu(), x + y, atol=1e-6)
+    got = K.bias_add(dev(y.clone()), dev(b))
+    assert torch.allclose(got.cpu(), y + b, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------- paged cache helpers
+
+PAGE = 64
+
+
+class Paged:
+    """Keys and values of a few sequences scattered over shuffled pages of a pool."""
+
+    def __init__(self, lens, nkv, hd, dtype, seed=0, extra_pages=3):
+        g = torch.Generator().manual_seed(seed)
+        self.lens, self.nkv, self.hd = lens, nkv, hd
+        self.k = [bf(torch.randn(n, nkv, hd, generator=g)) for n in lens]
+        self.v = [bf(torch.randn(n, nkv, hd, generator=g)) for n in lens]
+        n_pages = sum((n + PAGE - 1) // PAGE for n in lens) + extra_pages
+        order = list(range(n_pages))
+        random.Random(seed).shuffle(order)
+        width = max((n + PAGE - 1) // PAGE for n in lens) + 1
+        self.table = torch.full((len(lens), width), -1, dtype=torch.int32)
+        self.k_pool = torch.full((n_pages, nkv, PAGE, hd), 7.0)      # finite rubbish where nothing was written
+        self.v_pool = torch.full((n_pages, nkv, PAGE, hd), -7.0)
+        for b, n in enumerate(lens):
+            for pi in range((n + PAGE - 1) // PAGE):
+                self.table[b, pi] = order.pop()
+        self.dtype = dtype
+        self.write()
+
+    def write(self):
+        for b, n in enumerate(self.lens):
+            for pos in range(n):
+                pg = int(self.table[b, pos // PAGE])
+                self.k_pool[pg, :, pos % PAGE] = self.k[b][pos]
+                self.v_pool[pg, :, pos % PAGE] = self.v[b][pos]
+
+    def cuda(self):
+        return dev(self.k_pool.to(self.dtype)), dev(self.v_pool.to(self.dtype)), dev(self.table)
+
+
+def reference_attention(q_rows, paged, tok_row, tok_pos, nh, window):
+    """q_rows [T, nh, hd]; token t attends keys of sequence tok_row[t] up to tok_pos[t]."""
+    out = []
+    for t, (b, p) in enumerate(zip(tok_row, tok_pos)):
+        L = p + 1
+        q = torch.zeros(L, nh, paged.hd)
+        q[p] = q_rows[t]
+        out.append(plain.attention(q, paged.k[b][:L], paged.v[b][:L], window)[p])
+    return torch.stack(out)
+
+
+def attention_case(nh, nkv, hd, lens, window, seed):
+    """Queries for the last token of every sequence plus a few inner ones."""
+    tok_row, tok_pos = [], []
+    rng = random.Random(seed)
+    for b, n in enumerate(lens):
+        for p in sorted({n - 1, 0, rng.randrange(n), max(0, n - 2)}):
+            tok_row.append(b); tok_pos.append(p)
+    q = bf(rnd(len(tok_row), nh, hd, seed=seed + 1))
+    return q, tok_row, tok_pos
+
+
+CASES = [  # nh, nkv, hd, lens, window
+    (4, 2, 16, [5, 70, 129], None),
+    (3, 1, 32, [64, 1, 200], 32),
+    (14, 2, 64, [300, 65], None),
+    (6, 6, 48, [100], 17),
+    (5, 1, 128, [130, 40], 64),
+    (20, 1, 80, [90], None),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,window", CASES)
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_attention_generic(K, nh, nkv, hd, lens, window, dtype):
+    paged = Paged(lens, nkv, hd, DT[dtype], seed=hd)
+    q, tok_row, tok_pos = attention_case(nh, nkv, hd, lens, window, seed=nh)
+    kp, vp, table = paged.cuda()
+    got = K.attention_generic(dev(q.reshape(len(tok_row), -1).to(DT[dtype])), nh * hd, nh, nkv, hd, kp, vp, table,
+                              table.shape[1], dev(torch.tensor(tok_pos, dtype=torch.int32)),
+                              dev(torch.tensor(tok_row, dtype=torch.int32)), window, hd ** -0.5)
+    want = reference_attention(q, paged, tok_row, tok_pos, nh, window)
+    tol = 2e-5 if dtype == "f32" else 2e-2
+    assert torch.allclose(got.float().cpu(), want, atol=tol, rtol=tol), float((got.float().cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,window", CASES)
+@pytest.mark.parametrize("max_context", [None, 4096])
+def test_attention_decode(K, nh, nkv, hd, lens, window, max_context):
+    paged = Paged(lens, nkv, hd, torch.bfloat16, seed=hd + 1)
+    q, tok_row, tok_pos = attention_case(nh, nkv, hd, lens, window, seed=nh + 7)
+    kp, vp, table = paged.cuda()
+    # queries sit inside a wider row, as they do in the fused q/k/v buffer
+    stride = (nh + 2 * nkv) * hd
+    buf = torch.zeros(len(tok_row), stride)
+    buf[:, :nh * hd] = q.reshape(len(tok_row), -1)
+    got = K.attention_decode(dev(buf.to(torch.bfloat16)), stride, nh, nkv, hd, kp, vp, table, table.shape[1],
+                             dev(torch.tensor(tok_pos, dtype=torch.int32)), dev(torch.tensor(tok_row, dtype=torch.int32)),
+                             window, hd ** -0.5, max_context or max(lens))
+    want = reference_attention(q, paged, tok_row, tok_pos, nh, window)
+    assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2), float((got.float().cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,window", CASES)
+@pytest.mark.parametrize("cached", [0, 37])
+def test_attention_prefill(K, nh, nkv, hd, lens, window, cached):
+    """Every token of every sequence from position ``cached`` on, in one launch."""
+    paged = Paged(lens, nkv, hd, torch.bfloat16, seed=hd + 2)
+    starts = [min(cached, n - 1) for n in lens]
+    step_lens = [n - s for n, s in zip(lens, starts)]
+    tok_row = [b for b, n in enumerate(step_lens) for _ in range(n)]
+    tok_pos = [s + i for s, n in zip(starts, step_lens) for i in range(n)]
+    q = bf(rnd(len(tok_row), nh, hd, seed=5))
+    kp, vp, table = paged.cuda()
+    tiles = K.prefill_tiles(step_lens, starts, "cuda")
+    got = K.attention_prefill(dev(q.reshape(len(tok_row), -1).to(torch.bfloat16)), nh * hd, nh, nkv, hd, kp, vp, table,
+                              table.shape[1], tiles, len(tok_row), window, hd ** -0.5)
+    want = reference_attention(q, paged, tok_row, tok_pos, nh, window)
+    err = (got.float().cpu() - want).abs().max(dim=1).values
+    assert float(err.max()) < 2e-2, (float(err.max()), int(err.argmax()), tok_row[int(err.argmax())], tok_pos[int(err.argmax())])
+
+
+@pytest.mark.parametrize("kernel", ["generic_f32", "generic_bf16", "decode", "prefill"])
+def test_attention_finds_a_far_key_and_respects_the_windows_edge(K, kernel):
+    """One key among hundreds is made to dominate.  Without a window the output must be its
+    value; with a window ending just before it, it must not show; with one that just includes it, it must."""
+    nh, nkv, hd, n = 4, 2, 32, 333
+    dtype = torch.float32 if kernel == "generic_f32" else torch.bfloat16
+    far = 70                                                  # on the second page
+    for window, visible in ((None, True), (n - far, True), (n - far - 1, False)):
+        paged = Paged([n], nkv, hd, dtype, seed=11)
+        q = bf(rnd(1, nh, hd, seed=12))
+        paged.k[0][far, 1] = bf(30.0 * q[0, 3] / q[0, 3].norm())          # head 3 reads kv head 1
+        paged.write()
+        kp, vp, table = paged.cuda()
+        pos, row = dev(torch.tensor([n - 1], dtype=torch.int32)), dev(torch.tensor([0], dtype=torch.int32))
+        qd = dev(q.reshape(1, -1).to(dtype))
+        if kernel.startswith("generic"):
+            got = K.attention_generic(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], pos, row, window, 1.0)
+        elif kernel == "decode":
+            got = K.attention_decode(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], pos, row, window, 1.0, 512)
+        else:
+            tiles = K.prefill_tiles([1], [n - 1], "cuda")
+            got = K.attention_prefill(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], tiles, 1, window, 1.0)
+        head3 = got.float().cpu().view(nh, hd)[3]
+        hit = torch.allclose(head3, paged.v[0][far, 1], atol=3e-2)
+        assert hit == visible, (kernel, window, head3[:4], paged.v[0][far, 1][:4])
+
+
+# ---------------------------------------------------------------------------- rotary encoding and the cache write
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("nq,nkv,hd,theta", [(4, 2, 16, 1e4), (3, 1, 32, 1e6), (14, 2, 64, 1e6)])
+def test_rope_store(K, dtype, nq, nkv, hd, theta):
+    lens, starts = [3, 70], [62, 5]                            # rows continue from these lengths; the first crosses a page
+    tok_row = [b for b, n in enumerate(lens) for _ in range(n)]
+    tok_pos = [s + i for s, n in zip(starts, lens) for i in range(n)]
+    T = len(tok_row)
+    qkv = bf(rnd(T, (nq + 2 * nkv) * hd, seed=4))
+    cos, sin = plain.rope_angles(torch.arange(200), hd, theta)
+    table = torch.tensor([[2, 0, -1], [3, 1, 4]], dtype=torch.int32)
+    kp = torch.zeros(5, nkv, PAGE, hd, dtype=DT[dtype], device="cuda")
+    vp = torch.zeros_like(kp)
+    buf = dev(qkv.to(DT[dtype]))
+    K.rope_store(buf, nq, nkv, hd, dev(cos), dev(sin), dev(torch.tensor(tok_pos, dtype=torch.int32)),
+                 dev(torch.tensor(tok_row, dtype=torch.int32)), kp, vp, dev(table), 3)
+    c, s = cos[torch.tensor(tok_pos)], sin[torch.tensor(tok_pos)]
+    qk = plain.apply_rope(qkv[:, :(nq + nkv) * hd].view(T, nq + nkv, hd), c, s)
+    v = qkv[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    tol = 1e-5 if dtype == "f32" else 2e-2
+    got = buf.float().cpu()
+    assert torch.allclose(got[:, :(nq + nkv) * hd].view(T, nq + nkv, hd), qk, atol=tol, rtol=tol)
+    assert torch.equal(got[:, (nq + nkv) * hd:], qkv[:, (nq + nkv) * hd:])
+    kc, vc = kp.float().cpu(), vp.float().cpu()
+    for t, (b, p) in enumerate(zip(tok_row, tok_pos)):
+        pg = int(table[b, p // PAGE])
+        assert torch.allclose(kc[pg, :, p % PAGE], qk[t, nq:], atol=tol, rtol=tol), (t, b, p)
+        assert torch.equal(vc[pg, :, p % PAGE], v[t])
+    assert int((kc != 0).any(dim=-1).sum()) == T * nkv          # nothing else was touched
+    # no tables: nothing rotates, keys still reach the cache; no pools: nothing is stored
+    buf2 = dev(qkv.to(DT[dtype])); kp.zero_()
+    K.rope_store(buf2, nq, nkv, hd, None, None, dev(torch.tensor(tok_pos, dtype=torch.int32)),
+                 dev(torch.tensor(tok_row, dtype=torch.int32)), kp, vp, dev(table), 3)
+    assert torch.equal(buf2.float().cpu(), qkv) and int((kp != 0).any(dim=-1).sum()) == T * nkv
+
+
+# ---------------------------------------------------------------------------- matrix products
+
+@pytest.mark.parametrize("M,N,K_", [(1, 70, 45), (3, 64, 64), (77, 130, 96), (5, 1000, 352), (130, 96, 160)])
+@pytest.mark.parametrize("adt,wdt", [("f32", "f32"), ("bf16", "bf16"), ("bf16", "f32")])
+def test_linear_simt(K, M, N, K_, adt, wdt):
+    a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2)), bf(rnd(N, seed=3))
+    want = a.double() @ w.double().T
+    A, W = dev(a.to(DT[adt])), dev(w.to(DT[wdt]))
+    got = K.linear_simt(A, W, out_dtype=torch.float32)
+    assert torch.allclose(got.cpu().double(), want, atol=1e-4, rtol=1e-5)
+    got = K.linear_simt(A, W, dev(b), out_dtype=torch.bfloat16)
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu().double(), want + b.double(), atol=6e-2, rtol=1e-2)
+    x = rnd(M, N, seed=4)
+    got = K.linear_simt(A, W, dev(b), accumulate_into=dev(x.clone()))
+    assert torch.allclose(got.cpu().double(), x.double() + want + b.double(), atol=1e-4, rtol=1e-5)
+
+
+def test_linear_simt_rows_do_not_depend_on_their_neighbours(K):
+    a, w = rnd(70, 352, seed=1), rnd(96, 352, seed=2)
+    whole = K.linear_simt(dev(a), dev(w), out_dtype=torch.float32)
+    for r in (0, 13, 69):
+        assert torch.equal(K.linear_simt(dev(a[r:r + 1]), dev(w), out_dtype=torch.float32)[0], whole[r])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 64])
+@pytest.mark.parametrize("N,K_", [(100, 96), (896, 896), (1152, 896), (896, 4864), (9728, 896), (70, 160), (4000, 3584)])
+def test_linear_mma(K, M, N, K_):
+    a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
+    want = a.double() @ w.double().T
+    A, W = dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16))
+    assert K.linear_mma_takes(A, W)
+    got = K.linear_mma(A, W, out_dtype=torch.float32)
+    assert torch.allclose(got.cpu().double(), want, atol=1e-4, rtol=1e-4), float((got.cpu().double() - want).abs().max())
+    got = K.linear_mma(A, W, dev(b), out_dtype=torch.bfloat16)
+    assert torch.allclose(got.float().cpu().double(), want + b.double(), atol=4e-2, rtol=1e-2)
+    x = rnd(M, N, seed=4)
+    for _ in range(2):                                             # the tickets of the split ranges are left clean
+        got = K.linear_mma(A, W, dev(b), accumulate_into=dev(x.clone()))
+        assert torch.allclose(got.cpu().double(), x.double() + want + b.double(), atol=1e-4, rtol=1e-4)
+
+
+def test_linear_mma_rows_do_not_depend_on_their_neighbours(K):
+    a, w = bf(rnd(64, 4864, seed=1)), bf(rnd(896, 4864, seed=2, scale=0.02))
+    W = dev(w.to(torch.bfloat16))
+    whole = K.linear_mma(dev(a.to(torch.bfloat16)), W, out_dtype=torch.float32)
+    for rows in ([5], [0, 63], list(range(20, 29))):
+        part = K.linear_mma(dev(a[rows].to(torch.bfloat16)), W, out_dtype=torch.float32)
+        assert torch.equal(part, whole[rows])
+
+
+def test_linear_dispatch(K):
+    from pico_engine.ops import linear
+    a, w = bf(rnd(200, 96, seed=1)), bf(rnd(130, 96, seed=2))
+    want = a @ w.T
+    for adt, wdt, tol in (("bf16", "bf16", 5e-2), ("f32", "f32", 1e-4), ("bf16", "f32", 5e-2)):
+        got = linear(dev(a.to(DT[adt])), dev(w.to(DT[wdt])), out_dtype=DT[adt])
+        assert got.dtype == DT[adt] and torch.allclose(got.float().cpu(), want, atol=tol, rtol=1e-2)
+        x = rnd(200, 130, seed=5)
+        got = linear(dev(a.to(DT[adt])), dev(w.to(DT[wdt])), dev(w[:, 0].contiguous().to(DT[wdt])), accumulate_into=dev(x.clone()))
+        assert torch.allclose(got.cpu(), x + want + w[:, 0], atol=tol, rtol=1e-2)
+    got = linear(dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16)), out_dtype=torch.float32)
+    assert got.dtype == torch.float32
+
+
+# ---------------------------------------------------------------------------- sampling
+
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_argmax(K, V):
+    logits = rnd(5, V, seed=9)
+    logits[2, 17] = logits[2, 900] = 50.0                           # equal maxima: the first wins
+    logits[3, V - 1] = 60.0
+    got = K.argmax(dev(logits)).cpu().tolist()
+    assert got == logits.argmax(dim=-1).tolist() and got[2] == 17 and got[3] == V - 1
+
+
+@pytest.mark.parametrize("V", [257, 5000])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.8, 0, 1.0), (0.7, 0, 0.9), (1.3, 5, 1.0),
+                                                     (1.0, 40, 0.5), (0.5, 1, 1.0), (2.0, 0, 0.05)])
+def test_sample_equals_the_plain_sampler(K, V, temperature, top_k, top_p):
+    B = 24
+    logits = rnd(B, V, seed=V, scale=3.0)
+    request = torch.arange(B, dtype=torch.int32) + 3
+    step = torch.arange(B, dtype=torch.int32) * 2
+    got = K.sample(dev(logits), temperature, top_k, top_p, 1234, dev(request), dev(step)).cpu().tolist()
+    want = [plain.sample(logits[b], temperature, top_k, top_p, plain.uniform_for(1234, int(request[b]), int(step[b])))
+            for b in range(B)]
+    assert got == want
+    assert all(abs(K.draw_uniform(1234, r, s) - plain.uniform_for(1234, r, s)) == 0 for r in (0, 5) for s in (0, 9))
+
+
+def test_sample_draws_do_not_depend_on_the_batch(K):
+    logits = rnd(6, 777, seed=1, scale=2.0)
+    req, st = torch.tensor([4, 9, 1, 0, 7, 3], dtype=torch.int32), torch.tensor([0, 5, 2, 2, 1, 8], dtype=torch.int32)
+    whole = K.sample(dev(logits), 0.9, 0, 0.95, 5, dev(req), dev(st)).cpu()
+    for b in (0, 3, 5):
+        one = K.sample(dev(logits[b:b + 1]), 0.9, 0, 0.95, 5, dev(req[b:b + 1]), dev(st[b:b + 1])).cpu()
+        assert int(one[0]) == int(whole[b])
+    hist = torch.zeros(4)
+    peaked = torch.tensor([[0.0, math.log(2.0), math.log(4.0), math.log(1.0)]]).repeat(4000, 1)
+    draws = K.sample(dev(peaked), 1.0, 0, 1.0, 1, dev(torch.arange(4000, dtype=torch.int32)),
+                     dev(torch.zeros(4000, dtype=torch.int32))).cpu()
+    for i in range(4):
+        hist[i] = (draws == i).sum()
+    assert torch.allclose(hist / 4000, torch.tensor([1, 2, 4, 1]) / 8.0, atol=0.03)
