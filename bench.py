@@ -1,0 +1,168 @@
+"""The benchmark the build driver runs: decode tokens per second of the Qwen2.5-0.5B shape
+(random weights, bfloat16) at batch 8 and context 4096 on one B200, with the 2,048-token
+prefill, decode at batch 1 and 64, the end-to-end figure through ``Engine.generate`` and the
+roofline fractions on the same JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one decode step of the whole batch.  This library runs on one GPU: for
+``--gpus N`` with N > 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED, BATCH, CONTEXT, PREFILL_TOKENS = 2, 8, 4096, 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            if d.get("hbm_gbs") and d.get("bf16_tflops"):
+                return d, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Reads SM clocks and throttle reasons through NVML while the timed region runs (reading only)."""
+
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int = 0, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period_s, self._stop, self._thread, self._h, self._nvml = period_s, threading.Event(), None, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:                                   # noqa: BLE001 - no NVML: the record says so
+            self._nvml = None
+
+    def _read(self):
+        n = self._nvml
+        try:
+            self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
+                else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+            for bit, name in self.REASONS.items():
+                if bits & bit and name != "gpu_idle":
+                    self.reasons.add(name)
+        except Exception:                                   # noqa: BLE001
+            pass
+
+    def __enter__(self):
+        if self._nvml is not None:
+            def loop():
+                while not self._stop.is_set():
+                    self._read()
+                    self._stop.wait(self.period_s)
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def record(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable: NVML gave no sample"]}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def reference_arm() -> int:
+    """pico-engine itself cannot be run for this metric here; say why in one line."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "pico-engine loads only GGUF checkpoints with an embedded tokenizer (none is on this machine and "
+                      "there is no network), runs one sequence at a time and has no random-weights mode"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (recorded in config)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    from pico_engine import benchmark as B
+    from pico_engine.config import config_from_dict
+    from pico_engine.engine.engine import Engine
+
+    from pico_engine.config.shapes import shape
+    cfg_dict = shape("qwen2.5-0.5b")                       # BASELINE.json configs[2]
+    layers_full = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(cfg_dict)
+    eng = Engine.from_config(cfg, seed=SEED, draw_on="cuda", dtype="bfloat16", device="cuda:0", max_batch=64)
+    eng.ensure_cache(64 * CONTEXT, CONTEXT, max_seqs=64)
+    pk, pk_kind = peaks()
+
+    with ClockSampler() as clocks:
+        main_run = B.decode_device(eng, BATCH, CONTEXT, args.steps, warmup)
+    side_steps = min(args.steps, 128)
+    b1 = B.decode_device(eng, 1, CONTEXT, side_steps, warmup)
+    b64 = B.decode_device(eng, 64, CONTEXT, side_steps, warmup)
+    pre = B.prefill_device(eng, PREFILL_TOKENS)
+    e2e = B.decode_end_to_end(eng, BATCH, CONTEXT, min(args.steps, 256))
+
+    record = {
+        "metric": "decode tokens/s, batch 8, context 4096 (Qwen2.5-0.5B shape)", "value": main_run["tokens_per_s"],
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": main_run["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-0.5B shape, random weights seed 2", "global_batch": BATCH, "seq_len": CONTEXT,
+                   "parallelism": "none", "layers": cfg.num_hidden_layers, "layers_of_configuration": layers_full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied_head": cfg.tie_word_embeddings, "prefill_tokens": PREFILL_TOKENS, "cuda_graph": main_run["graph"],
+                   "l2": "each step reads 0.99 GB of weights, more than the 126 MB L2",
+                   "context_during_timing": f"{CONTEXT - args.steps + 1}..{CONTEXT}", "peaks": pk_kind},
+        "e2e": {"value": e2e["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": e2e["ms_per_step"]},
+        "gpu_launches": main_run["launches_per_step"] * args.steps,
+        "prefill": {"value": pre["tokens_per_s"], "tokens": pre["tokens"], "ms": pre["ms"],
+                    "frac": pre["tflops_per_s"] / pk["bf16_tflops"]},
+        "roofline": {"bound": "hbm", "achieved": main_run["gbytes_per_s"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": main_run["gbytes_per_s"] / pk["hbm_gbs"]},
+        "points": {"decode_b1": b1["tokens_per_s"], "decode_b64": b64["tokens_per_s"],
+                   "decode_b1_hbm_frac": b1["gbytes_per_s"] / pk["hbm_gbs"],
+                   "decode_b64_hbm_frac": b64["gbytes_per_s"] / pk["hbm_gbs"]},
+        "clocks": clocks.record(),
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

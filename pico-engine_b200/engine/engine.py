@@ -8,6 +8,7 @@ tokenizer here), ``generate`` also takes a batch of prompts, and draws are seede
 from __future__ import annotations
 
 import os
+import time
 from typing import Iterable, List, Optional, Sequence, Union
 
 import torch
@@ -65,6 +66,7 @@ class Engine:
         self.cache: Optional[Cache] = None
         self.stepper: Optional[Stepper] = None
         self._graphs = {}
+        self.last_timing = {}                     # host-clock seconds of the last generate call, by phase
 
     @classmethod
     def from_config(cls, config, seed: int = 0, draw_on="cpu", **kwargs) -> "Engine":
@@ -115,6 +117,7 @@ class Engine:
             need = [held_tokens(r) for r in probe]
             budget = self._want_tokens or sum(sorted(need, reverse=True)[:self.max_batch])
             self.ensure_cache(max(budget, max(need)), max(len(r.prompt) + r.max_new_tokens for r in probe))
+        self.last_timing = {"prefill_s": 0.0, "decode_s": 0.0, "decode_steps": 0, "h2d_bytes": 0}
         backend = EngineBackend(self, Sampler(params), use_graph)
         budget = self.cache.n_pages * PAGE if self.cache is not None else PAGE
         return run_generation(backend, prompts, mnt, stop, self.max_batch, budget)
@@ -137,16 +140,27 @@ class EngineBackend:
         return torch.tensor(list(values), dtype=torch.int32).to(self.e.device, non_blocking=True)
 
     def prefill(self, slots, prompts, requests) -> List[int]:
+        t0 = time.perf_counter()
         logits = self.e.stepper.step(slots, prompts)
-        chosen = self.sampler.choose(logits, self._int32(requests), self._int32([0] * len(slots)))
-        return chosen.tolist()
+        chosen = self.sampler.choose(logits, self._int32(requests), self._int32([0] * len(slots))).tolist()
+        self.e.last_timing["prefill_s"] += time.perf_counter() - t0
+        return chosen
 
     def decode(self, slots, tokens, requests, steps) -> List[int]:
+        """One token per sequence in, one chosen token per sequence out, both on the host: the
+        step's description is copied from pinned memory, the result is read back."""
+        t0, sent = time.perf_counter(), self.e.stepper.h2d_bytes
         if self.use_graph:
             key = (len(slots), self.sampler.params)
             g = self.e._graphs.get(key)
             if g is None:
                 g = self.e._graphs[key] = GraphedDecode(self.e.stepper, self.sampler, len(slots))
-            return g.run(slots, tokens, requests, steps).tolist()
-        logits = self.e.stepper.step(slots, [[t] for t in tokens])
-        return self.sampler.choose(logits, self._int32(requests), self._int32(steps)).tolist()
+            chosen = g.run(slots, tokens, requests, steps).tolist()
+        else:
+            logits = self.e.stepper.step(slots, [[t] for t in tokens])
+            chosen = self.sampler.choose(logits, self._int32(requests), self._int32(steps)).tolist()
+        t = self.e.last_timing
+        t["decode_s"] += time.perf_counter() - t0
+        t["decode_steps"] += 1
+        t["h2d_bytes"] += self.e.stepper.h2d_bytes - sent
+        return chosen

@@ -67,6 +67,7 @@ class Stepper:
         self.vocab = model.plan.vocab_size
         self._ring: List[list] = [[None, None] for _ in range(4)]     # pinned staging buffers and their copy events
         self._ring_at = 0
+        self.h2d_bytes = 0                        # bytes of step descriptions copied to the device so far
 
     # ------------------------------------------------------------------ building a step
     def _stage(self, host: np.ndarray):
@@ -150,6 +151,7 @@ class Stepper:
 
     def upload(self, host: np.ndarray, dev: Optional[torch.Tensor] = None) -> torch.Tensor:
         slot, staged = self._stage(host)
+        self.h2d_bytes += int(host.nbytes)
         if dev is None:
             dev = torch.empty(host.shape[0], dtype=torch.int32, device=self.device)
         dev[:host.shape[0]].copy_(staged, non_blocking=True)

@@ -258,7 +258,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
     check(lib.pe_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
                                   n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context), ws,
-                                  stream_ptr()), "attention_decode")
+                                  stream_ptr()), "attention_decode", 2 if nbytes else 1)
     return out
 
 

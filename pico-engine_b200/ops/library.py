@@ -85,8 +85,12 @@ def for_head_dim(head_dim: int) -> ctypes.CDLL:
     return lib
 
 
-def check(code: int, name: str) -> None:
+LAUNCHES = [0]      # kernels of this library launched so far (a captured launch counts once, when it is captured)
+
+
+def check(code: int, name: str, kernels: int = 1) -> None:
     if code == 0:
+        LAUNCHES[0] += kernels
         return
     if code == 10001:
         raise KernelError(f"{name}: sizes or dtypes that this kernel does not take")

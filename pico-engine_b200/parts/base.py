@@ -83,6 +83,10 @@ class Part:
     def prepare(self, max_positions: int) -> None:
         """Called once before the first step, with the longest sequence the cache can hold."""
 
+    def weights(self) -> List[torch.Tensor]:
+        """The tensors a step reads in full (for traffic accounting)."""
+        return [v for v in vars(self).values() if isinstance(v, torch.Tensor)]
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows_index: Optional[torch.Tensor] = None) -> torch.Tensor:

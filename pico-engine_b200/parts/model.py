@@ -74,12 +74,14 @@ class DecoderModel:
     def forward(self, token_ids: torch.Tensor, ctx: StepContext, rows_index: torch.Tensor) -> torch.Tensor:
         return self.logits(self.hidden(token_ids, ctx), rows_index)
 
-    def weight_bytes(self) -> int:
+    def step_weight_bytes(self) -> int:
+        """Bytes of weights a step reads in full: every matrix and vector of every executed layer
+        and the head; the embedding table only where it is the head too (a lookup reads a row a token)."""
         seen, total = set(), 0
-        tensors = [self.embedding, self.head]
-        for part in self._parts():
-            tensors.extend(v for v in vars(part).values() if isinstance(v, torch.Tensor))
-            pos = getattr(part, "position", None)
+        tensors = [self.head] + list(self.final_norm.weights())
+        for entry in self.plan.schedule:
+            for part in self.layers[entry.layer].parts():
+                tensors.extend(part.weights())
         for t in tensors:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())

@@ -27,6 +27,9 @@ class RotaryHalf(Position):
         self.cos = angles.cos().to(self.device).contiguous()
         self.sin = angles.sin().to(self.device).contiguous()
 
+    def weights(self):
+        return []                      # the tables are read by position, a few rows a step
+
     def rotate_and_store(self, qkv, n_q, n_kv, head_dim, ctx, kv):
         if ctx.max_context > self.cos.shape[0]:
             raise ValueError(f"a sequence reaches position {ctx.max_context - 1}, the rotary tables hold "
