@@ -56,25 +56,37 @@ __global__ void __launch_bounds__(32 * AD_WARPS) attention_decode_kernel(
         for (int r = 0; r < 4; ++r) acc[c][r][0] = acc[c][r][1] = acc[c][r][2] = acc[c][r][3] = 0.f;
 
     const int begin = max(lo, split * split_len), end = min(pos + 1, (split + 1) * split_len);
-    for (int tile = begin / 16 + warp; tile * 16 < end; tile += AD_WARPS) {
-        const int key0 = tile * 16;
-        const int page = table[key0 / PE_PAGE];
-        if (page < 0) continue;                           // a page the window has left behind
-        const size_t base = (((size_t)page * nkv + kvh) * PE_PAGE + (key0 % PE_PAGE)) * AD_HD;
-
-        AmTile kv;
-        am_load_tile(kv, k_pool, v_pool, base, g, t);
-        float s[2][4];
-        am_scores(s, qf, kv);
-        // s[j][e]: row (e & 2 ? g + 8 : g), key key0 + j*8 + 2t + (e & 1)
+    // software pipeline: the loads of the warp's next tile are in flight while the current one is used
+    AmTile cur, next;
+    bool cur_ok = false, next_ok = false;
+    auto fetch = [&](AmTile& dst, int tl, bool& ok) {
+        ok = false;
+        if (tl * 16 >= end) return;
+        const int page = table[tl * 16 / PE_PAGE];
+        if (page < 0) return;                             // a page the window has left behind
+        am_load_tile(dst, k_pool, v_pool, (((size_t)page * nkv + kvh) * PE_PAGE + (tl * 16 % PE_PAGE)) * AD_HD, g, t);
+        ok = true;
+    };
+    int tile = begin / 16 + warp;
+    fetch(cur, tile, cur_ok);
+    for (; tile * 16 < end; tile += AD_WARPS) {
+        fetch(next, tile + AD_WARPS, next_ok);
+        if (cur_ok) {
+            const int key0 = tile * 16;
+            float s[2][4];
+            am_scores(s, qf, cur);
+            // s[j][e]: row (e & 2 ? g + 8 : g), key key0 + j*8 + 2t + (e & 1)
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+            for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = key0 + j * 8 + 2 * t + (e & 1);
-                s[j][e] = (key >= begin && key < end) ? s[j][e] * scale_log2e : -INFINITY;
-            }
-        am_softmax_accumulate(s, m_run, l_run, acc, kv);
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + 2 * t + (e & 1);
+                    s[j][e] = (key >= begin && key < end) ? s[j][e] * scale_log2e : -INFINITY;
+                }
+            am_softmax_accumulate(s, m_run, l_run, acc, cur);
+        }
+        cur = next;
+        cur_ok = next_ok;
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -148,7 +160,7 @@ extern "C" int pe_attention_decode_head_dim() { return AD_HD; }
 // only, never of the sequences' lengths (the same launch is replayed as sequences grow).
 extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_context, int* split_len_out) {
     const int G = nh / nkv, ctas = T * nkv * ((G + 15) / 16);
-    int want = (2 * 148 + ctas - 1) / ctas;
+    int want = (4 * 148 + ctas - 1) / ctas;
     const int most = (max_context + PE_PAGE - 1) / PE_PAGE;
     if (want > most) want = most;
     if (want > 64) want = 64;

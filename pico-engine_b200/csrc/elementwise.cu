@@ -33,17 +33,42 @@ extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, floa
 // ---------------------------------------------------------------- RMSNorm
 // One block per output row.  `rows_index` (may be null) picks the input row of each output
 // row, so the final norm runs only on the rows whose logits are wanted.
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<unsigned*>(&lo); v.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(o) = v;
+}
+
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
                                const void* __restrict__ w, int w_dtype, float eps, TO* __restrict__ out, int H) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows_index ? rows_index[r] : r) * H;
+    TO* o = out + (size_t)r * H;
     float ss = 0.f;
+    if ((H & 3) == 0) {                                       // rows start on 16-byte boundaries
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+            const float4 v = x4[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+        for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+            const float4 v = x4[i];
+            store4(o + 4 * i, v.x * rstd * load_as_f(w, w_dtype, 4 * i), v.y * rstd * load_as_f(w, w_dtype, 4 * i + 1),
+                   v.z * rstd * load_as_f(w, w_dtype, 4 * i + 2), v.w * rstd * load_as_f(w, w_dtype, 4 * i + 3));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
     ss = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
-    TO* o = out + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(xr[i] * rstd * load_as_f(w, w_dtype, i));
 }
 
@@ -51,7 +76,7 @@ extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, 
                           int out_dtype, int rows, int H, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = H >= 2048 ? 512 : 256;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (out_dtype == PE_F32) rmsnorm_kernel<float><<<rows, threads, 0, s>>>(x, rows_index, w, w_dtype, eps, (float*)out, H);
     else if (out_dtype == PE_BF16) rmsnorm_kernel<bf16><<<rows, threads, 0, s>>>(x, rows_index, w, w_dtype, eps, (bf16*)out, H);
     else return PE_ERR_UNSUPPORTED;
@@ -61,13 +86,33 @@ extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, 
 
 // ---------------------------------------------------------------- SwiGLU
 // gu is [T, 2I]: gate in the first I columns, up in the last I.  out[t, i] = silu(gate) * up.
+__device__ __forceinline__ float silu_mul(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
+
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
-        const float g = to_f(gu[t * 2 * I + i]), u = to_f(gu[t * 2 * I + I + i]);
-        const float sig = 1.0f / (1.0f + expf(-g));
-        out[idx] = from_f<T>(g * sig * u);
+        out[idx] = from_f<T>(silu_mul(to_f(gu[t * 2 * I + i]), to_f(gu[t * 2 * I + I + i])));
+    }
+}
+
+// I a multiple of 8: eight bfloat16 per thread with 16-byte loads and stores
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t groups) {
+    const int per_row = I / 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / per_row, i = (idx % per_row) * 8;
+        const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+        const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
+            o2[e] = __floats2bfloat162_rn(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+        }
+        *reinterpret_cast<uint4*>(out + t * I + i) = o;
     }
 }
 
@@ -75,6 +120,13 @@ extern "C" int pe_swiglu(const void* gu, void* out, int dtype, int T, int I, voi
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)T * I;
+    if (dtype == PE_BF16 && I % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
+        const size_t groups = total / 8;
+        const int blocks = (int)((groups + 255) / 256 < 148 * 16 ? (groups + 255) / 256 : 148 * 16);
+        swiglu_bf16x8_kernel<<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, groups);
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == PE_F32) swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, total);
     else if (dtype == PE_BF16) swiglu_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
@@ -91,9 +143,36 @@ __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__
         x[i] += to_f(y[i]);
 }
 
+__device__ __forceinline__ float4 load4_as_f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_as_f(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// total a multiple of 4, both pointers aligned for 4-element accesses
+template <typename T>
+__global__ void residual_add_x4_kernel(float* __restrict__ x, const T* __restrict__ y, size_t groups) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = *reinterpret_cast<float4*>(x + 4 * i);
+        const float4 b = load4_as_f(y + 4 * i);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        *reinterpret_cast<float4*>(x + 4 * i) = a;
+    }
+}
+
 extern "C" int pe_residual_add(float* x, const void* y, int y_dtype, long long total, void* stream) {
     if (total <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (total % 4 == 0 && !(((uintptr_t)x | (uintptr_t)y) & 15) && (y_dtype == PE_F32 || y_dtype == PE_BF16)) {
+        const long long groups = total / 4, wantg = (groups + 255) / 256;
+        const int blocksg = (int)(wantg < 148 * 16 ? wantg : 148 * 16);
+        if (y_dtype == PE_F32) residual_add_x4_kernel<float><<<blocksg, 256, 0, s>>>(x, (const float*)y, (size_t)groups);
+        else residual_add_x4_kernel<bf16><<<blocksg, 256, 0, s>>>(x, (const bf16*)y, (size_t)groups);
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (y_dtype == PE_F32) residual_add_kernel<float><<<blocks, 256, 0, s>>>(x, (const float*)y, (size_t)total);

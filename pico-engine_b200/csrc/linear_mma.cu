@@ -1,24 +1,27 @@
 // out[M, N] = A[M, K] . W[N, K]^T (+ bias) for few rows M (decoding: one row per sequence),
 // bfloat16 operands, float32 accumulation on the tensor cores (mma.sync m16n8k16).
 //
-// With few rows the product is bound by reading W once.  The roles are therefore swapped:
-// 16 rows of W are the M side of the MMA, 8 rows of A (8 sequences) its N side.  A warp owns
-// 16 rows of W and streams them from global memory straight into MMA fragments with 16-byte
-// loads (the k index inside a 32-wide chunk is permuted identically for both operands, which
-// a dot product does not notice); A is small and is read through L1.  No shared memory, no
-// barrier inside the k loop.
+// With few rows the product is bound by reading W once, and for the small matrices of a
+// decoder layer by memory latency: the whole matrix has to be in flight at once.  The roles
+// are therefore swapped (16 rows of W are the M side of the MMA, 8 rows of A its N side), and
+// a CTA of eight warps owns 16 rows of W over a range of K: the warps take the 32-wide k steps
+// of that range in turn, each issuing the 16-byte loads of four steps (straight into MMA
+// fragments, the k index inside a step permuted identically for both operands) before it
+// uses any of them.  A is small and is read through L1/L2.  The warps' partial sums are added
+// in shared memory in the order of the warps.
 //
-// K is cut into `splits` ranges so that small matrices still fill the GPU; each CTA writes
-// its partial sums to scratch, and the CTA that finishes last for a tile of rows adds the
-// partials in the order of the ranges and applies the epilogue.  `splits` depends on N and
-// K only, so a row's result does not depend on how many rows are beside it.
+// For matrices with few rows K is also cut into `splits` ranges over several CTAs; each
+// writes its sums to scratch, and the CTA that finishes last for its 16 rows adds them in the
+// order of the ranges and applies the epilogue.  `splits` depends on N and K only, so a row's
+// result does not depend on how many rows are beside it.
 //
 // pico-engine leaves decode products to float32 cuBLAS (src/pico_engine/model.py:148-150, 177,
 // 213, 223, 235) or its quantized Triton GEMVs (src/pico_engine/kernels.py:161-344).
 #include "common.cuh"
 
-#define LM_WARPS 4
-#define LM_ROWS (16 * LM_WARPS)        // rows of W per CTA
+#define LM_WARPS 8
+#define LM_ROWS 16                     // rows of W per CTA
+#define LM_UNROLL 4                    // k steps whose loads a warp has in flight
 #define LM_MAX_M 64
 #define LM_MAX_SPLITS 16
 
@@ -49,11 +52,13 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
     const bf16* __restrict__ A, const bf16* __restrict__ W, const void* __restrict__ bias, int bias_dtype,
     void* __restrict__ out, int epilogue, int M, int N, int K, int splits, int k_per_split,
     float* __restrict__ partial, unsigned int* __restrict__ tickets) {
+    __shared__ float red[LM_WARPS][NT * 4][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * LM_ROWS + warp * 16;
+    const int n0 = blockIdx.x * LM_ROWS;
     const int split = blockIdx.y;
     const int k_begin = split * k_per_split;
     const int k_end = min(K, k_begin + k_per_split);
+    const int n_steps = (k_end - k_begin + 31) / 32;
 
     float acc[NT][4];
 #pragma unroll
@@ -65,51 +70,51 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
     const bf16* w1 = W + (size_t)(ok1 ? r1 : 0) * K;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    if (n0 < N) {
-#pragma unroll 4
-        for (int kb = k_begin; kb < k_end; kb += 32) {
-            const int k = kb + t * 8;
-            const bool kin = k < k_end;                      // K and k_per_split are multiples of 8
-            const uint4 wa = (ok0 && kin) ? ldg_stream(w0 + k) : zero;
-            const uint4 wb = (ok1 && kin) ? ldg_stream(w1 + k) : zero;
+    for (int base = warp; base < n_steps; base += LM_WARPS * LM_UNROLL) {
+        uint4 wa[LM_UNROLL], wb[LM_UNROLL];
+#pragma unroll
+        for (int u = 0; u < LM_UNROLL; ++u) {              // all loads of W first: they are what the kernel waits for
+            const int k = k_begin + (base + u * LM_WARPS) * 32 + t * 8;
+            const bool kin = k < k_end;                    // K and k_per_split are multiples of 8
+            wa[u] = (ok0 && kin) ? ldg_stream(w0 + k) : zero;
+            wb[u] = (ok1 && kin) ? ldg_stream(w1 + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < LM_UNROLL; ++u) {
+            const int k = k_begin + (base + u * LM_WARPS) * 32 + t * 8;
+            const bool kin = k < k_end;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int m = j * 8 + g;
                 const uint4 a = (m < M && kin) ? __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * K + k)) : zero;
-                mma_bf16(acc[j], wa.x, wb.x, wa.y, wb.y, a.x, a.y);
-                mma_bf16(acc[j], wa.z, wb.z, wa.w, wb.w, a.z, a.w);
+                mma_bf16(acc[j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
+                mma_bf16(acc[j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
             }
         }
     }
 
-    // acc[j][0]: (W row n0+g, A row j*8+2t), [1]: (n0+g, j*8+2t+1), [2]: (n0+g+8, j*8+2t), [3]: (n0+g+8, j*8+2t+1)
-    if (splits == 1) {
-        if (n0 < N) {
+    // acc[j][e] of lane (g, t): W row n0 + g + (e & 2 ? 8 : 0), A row j*8 + 2t + (e & 1)
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
+    for (int j = 0; j < NT; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int n = (e & 2) ? r1 : r0, m = j * 8 + 2 * t + (e & 1);
-                    if (n < N && m < M) {
-                        float v = acc[j][e];
-                        if (bias) v += load_as_f(bias, bias_dtype, n);
-                        lm_store(out, epilogue, (size_t)m * N + n, v);
-                    }
-                }
+        for (int e = 0; e < 4; ++e) red[warp][j * 4 + e][lane] = acc[j][e];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += 32 * LM_WARPS) {
+        const int je = idx >> 5, ln = idx & 31;
+        const int n = n0 + (ln >> 2) + ((je & 2) ? 8 : 0), m = (je >> 2) * 8 + 2 * (ln & 3) + (je & 1);
+        if (n >= N || m >= M) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < LM_WARPS; ++w) v += red[w][je][ln];
+        if (splits == 1) {
+            if (bias) v += load_as_f(bias, bias_dtype, n);
+            lm_store(out, epilogue, (size_t)m * N + n, v);
+        } else {
+            partial[((size_t)split * M + m) * N + n] = v;
         }
-        return;
     }
+    if (splits == 1) return;
 
-    // partial[split][m][n]
-    if (n0 < N) {
-#pragma unroll
-        for (int j = 0; j < NT; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int n = (e & 2) ? r1 : r0, m = j * 8 + 2 * t + (e & 1);
-                if (n < N && m < M) partial[((size_t)split * M + m) * N + n] = acc[j][e];
-            }
-    }
     __shared__ unsigned int s_last;
     __threadfence();
     __syncthreads();
@@ -120,9 +125,9 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const int rows = min(LM_ROWS, N - blockIdx.x * LM_ROWS);
+    const int rows = min(LM_ROWS, N - n0);
     for (int idx = threadIdx.x; idx < rows * M; idx += blockDim.x) {
-        const int m = idx / rows, n = blockIdx.x * LM_ROWS + idx % rows;
+        const int m = idx / rows, n = n0 + idx % rows;
         float v = 0.f;
         for (int s = 0; s < splits; ++s) v += __ldcg(&partial[((size_t)s * M + m) * N + n]);
         if (bias) v += load_as_f(bias, bias_dtype, n);
@@ -131,13 +136,14 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
     if (threadIdx.x == 0) tickets[blockIdx.x] = 0u;          // ready for the next launch
 }
 
-// The number of K ranges for an [N, K] weight: enough CTAs to occupy the GPU, at least 128
-// columns each.  A function of N and K only.
+// The number of K ranges for an [N, K] weight: about two CTAs per SM for matrices with few
+// rows, at least 256 columns each.  A function of N and K only.
 extern "C" int pe_linear_mma_splits(int N, int K) {
     const int tiles = (N + LM_ROWS - 1) / LM_ROWS;
-    int s = 1;
-    while (s < LM_MAX_SPLITS && tiles * s < 2 * 148 && K / (s * 2) >= 128) s *= 2;
-    return s;
+    int s = (2 * 148 + tiles - 1) / tiles;
+    if (s > K / 256) s = K / 256;
+    if (s > LM_MAX_SPLITS) s = LM_MAX_SPLITS;
+    return s < 1 ? 1 : s;
 }
 
 extern "C" long long pe_linear_mma_scratch_bytes(int M, int N, int K) {
@@ -145,7 +151,7 @@ extern "C" long long pe_linear_mma_scratch_bytes(int M, int N, int K) {
     return s > 1 ? (long long)s * M * N * 4 : 0;
 }
 
-// `tickets` holds at least ceil(N / 64) zeroed unsigned ints; the kernel leaves them zero.
+// `tickets` holds at least ceil(N / 16) zeroed unsigned ints; the kernel leaves them zero.
 extern "C" int pe_linear_mma(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int epilogue,
                              int M, int N, int K, void* partial, void* tickets, void* stream) {
     if (M <= 0 || N <= 0) return 0;

@@ -51,43 +51,72 @@ __device__ __forceinline__ int block_sum_i(int v, int* scratch) {
 }
 
 // ---------------------------------------------------------------- argmax (lowest index among equal maxima)
-__global__ void __launch_bounds__(SP_THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
-    __shared__ float vals[32];
-    __shared__ int idxs[32];
-    const float* row = logits + (size_t)blockIdx.x * V;
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < bi) || bi == 0x7fffffff) { best = v; bi = i; }
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Two stages so that one row of a large vocabulary is read by many blocks: each block reduces a
+// chunk to one 64-bit word (ordered key of the value, then the complemented index, so that the
+// maximum word is the largest value at its lowest index), a second kernel reduces the words.
+#define AX_THREADS 256
+#define AX_CHUNK 2048
+
+__device__ __forceinline__ unsigned long long ax_pack(float v, int idx) {
+    return ((unsigned long long)order_key(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
+}
+__device__ __forceinline__ unsigned long long ax_warp_max(unsigned long long v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = other > v ? other : v;
     }
-    if (lane == 0) { vals[warp] = best; idxs[warp] = bi; }
+    return v;
+}
+__device__ __forceinline__ unsigned long long ax_block_max(unsigned long long v, unsigned long long* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = ax_warp_max(v);
+    if (lane == 0) scratch[warp] = v;
     __syncthreads();
     if (warp == 0) {
-        const int nwarps = blockDim.x >> 5;
-        best = lane < nwarps ? vals[lane] : -INFINITY;
-        bi = lane < nwarps ? idxs[lane] : 0x7fffffff;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
-        }
-        if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+        v = lane < nwarps ? scratch[lane] : 0ull;
+        v = ax_warp_max(v);
     }
+    return v;                                                 // valid in warp 0
 }
 
-extern "C" int pe_argmax(const float* logits, int* out, int B, int V, void* stream) {
+__global__ void __launch_bounds__(AX_THREADS) argmax_partial_kernel(const float* __restrict__ logits, int V, int chunks,
+                                                                    unsigned long long* __restrict__ part) {
+    __shared__ unsigned long long scratch[32];
+    const int b = blockIdx.y, c = blockIdx.x;
+    const float* row = logits + (size_t)b * V;
+    const int begin = c * AX_CHUNK, end = min(V, begin + AX_CHUNK);
+    unsigned long long best = 0ull;
+    for (int i = begin + threadIdx.x; i < end; i += AX_THREADS) {
+        const unsigned long long p = ax_pack(row[i], i);
+        best = p > best ? p : best;
+    }
+    best = ax_block_max(best, scratch);
+    if (threadIdx.x == 0) part[(size_t)b * chunks + c] = best;
+}
+
+__global__ void __launch_bounds__(AX_THREADS) argmax_final_kernel(const unsigned long long* __restrict__ part, int chunks,
+                                                                  int* __restrict__ out) {
+    __shared__ unsigned long long scratch[32];
+    unsigned long long best = 0ull;
+    for (int i = threadIdx.x; i < chunks; i += AX_THREADS) {
+        const unsigned long long p = part[(size_t)blockIdx.x * chunks + i];
+        best = p > best ? p : best;
+    }
+    best = ax_block_max(best, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(best & 0xFFFFFFFFull));
+}
+
+extern "C" long long pe_argmax_scratch_bytes(int B, int V) { return (long long)B * ((V + AX_CHUNK - 1) / AX_CHUNK) * 8; }
+
+extern "C" int pe_argmax(const float* logits, int* out, int B, int V, void* scratch, void* stream) {
     if (B <= 0) return 0;
-    if (V <= 0) return PE_ERR_UNSUPPORTED;
-    argmax_kernel<<<B, SP_THREADS, 0, (cudaStream_t)stream>>>(logits, out, V);
+    if (V <= 0 || B > 65535 || !scratch) return PE_ERR_UNSUPPORTED;
+    const int chunks = (V + AX_CHUNK - 1) / AX_CHUNK;
+    cudaStream_t s = (cudaStream_t)stream;
+    argmax_partial_kernel<<<dim3(chunks, B), AX_THREADS, 0, s>>>(logits, V, chunks, (unsigned long long*)scratch);
+    PE_LAUNCH_CHECK();
+    argmax_final_kernel<<<B, AX_THREADS, 0, s>>>((const unsigned long long*)scratch, chunks, out);
     PE_LAUNCH_CHECK();
     return 0;
 }

@@ -116,7 +116,7 @@ class Engine:
         if probe:
             need = [held_tokens(r) for r in probe]
             budget = self._want_tokens or sum(sorted(need, reverse=True)[:self.max_batch])
-            self.ensure_cache(max(budget, max(need)), max(len(r.prompt) + r.max_new_tokens for r in probe))
+            self.ensure_cache(max(budget, max(need)), max(len(r.prompt) + max(r.max_new_tokens - 1, 0) for r in probe))
         self.last_timing = {"prefill_s": 0.0, "decode_s": 0.0, "decode_steps": 0, "h2d_bytes": 0}
         backend = EngineBackend(self, Sampler(params), use_graph)
         budget = self.cache.n_pages * PAGE if self.cache is not None else PAGE

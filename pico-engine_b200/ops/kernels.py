@@ -172,7 +172,10 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     if out is None:
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, (B,))
-    check(core().pe_argmax(logits.data_ptr(), out.data_ptr(), B, V, stream_ptr()), "argmax")
+    from .workspace import scratch
+    lib = core()
+    ws = scratch("argmax.partial", lib.pe_argmax_scratch_bytes(B, V), logits.device)
+    check(lib.pe_argmax(logits.data_ptr(), out.data_ptr(), B, V, ws.data_ptr(), stream_ptr()), "argmax", 2)
     return out
 
 
@@ -229,7 +232,7 @@ def linear_mma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
     partial = tickets = None
     if lib.pe_linear_mma_splits(N, K) > 1:
         partial = scratch("linear_mma.partial", lib.pe_linear_mma_scratch_bytes(64, N, K), a.device).data_ptr()
-        tickets = scratch("linear_mma.tickets", 4 * ((N + 63) // 64), a.device, zeroed=True).data_ptr()
+        tickets = scratch("linear_mma.tickets", 4 * ((N + 15) // 16), a.device, zeroed=True).data_ptr()
     check(lib.pe_linear_mma(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
                             out.data_ptr(), epilogue, M, N, K, partial, tickets, stream_ptr()), "linear_mma")
     return out

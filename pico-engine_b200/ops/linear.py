@@ -26,12 +26,13 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         M = a.shape[0]
         if M <= SMALL_M and kernels.linear_mma_takes(a, w):
             return kernels.linear_mma(a, w, bias, out_dtype, accumulate_into)
-        y = torch.mm(a, w.t())
-        if accumulate_into is not None:
+        if bias is not None and bias.dtype == a.dtype:
+            y = torch.addmm(bias, a, w.t())                  # the library adds the bias in its epilogue
+        else:
+            y = torch.mm(a, w.t())
             if bias is not None:
                 kernels.bias_add(y, bias)
+        if accumulate_into is not None:
             return kernels.residual_add(accumulate_into, y)
-        if bias is not None:
-            kernels.bias_add(y, bias)
         return y if (out_dtype or a.dtype) == y.dtype else y.to(out_dtype)
     return kernels.linear_simt(a, w, bias, out_dtype, accumulate_into)
