@@ -23,10 +23,12 @@
 #define AD_ROW (AD_HD + 2)                 // floats per merged row in shared memory: O, max, sum
 
 __global__ void __launch_bounds__(32 * AD_WARPS) attention_decode_kernel(
-    const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
-    const int* __restrict__ block_table, int table_stride, const int* __restrict__ tok_pos,
-    const int* __restrict__ tok_row, int nh, int nkv, int window, float scale_log2e, int split_len, int n_splits,
-    float* __restrict__ part, bf16* __restrict__ out) {
+    const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool,
+    const int* block_table, int table_stride, const int* tok_pos,
+    const int* tok_row, int nh, int nkv, int window, float scale_log2e, int split_len, int n_splits,
+    float* part, bf16* out) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];                       // [AD_WARPS][16][AD_ROW]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int tok = blockIdx.x, split = blockIdx.z;
@@ -137,7 +139,9 @@ __global__ void __launch_bounds__(32 * AD_WARPS) attention_decode_kernel(
 }
 
 // out[token][head][:] from the partials of all key ranges, added in the order of the ranges.
-__global__ void attention_decode_merge_kernel(const float* __restrict__ part, int n_splits, bf16* __restrict__ out) {
+__global__ void attention_decode_merge_kernel(const float* part, int n_splits, bf16* out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t th = blockIdx.x;                          // token * nh + head
     const float* src = part + th * n_splits * AD_ROW;
     float m = -INFINITY;
@@ -155,6 +159,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part, in
 }
 
 extern "C" int pe_attention_decode_head_dim() { return AD_HD; }
+extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }
 
 // How many key ranges a launch over `max_context` keys uses: a function of the launch shape
 // only, never of the sequences' lengths (the same launch is replayed as sequences grow).
@@ -195,13 +200,13 @@ extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const
     }
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nkv * ((G + 15) / 16), n_splits);
-    attention_decode_kernel<<<grid, 32 * AD_WARPS, smem, s>>>(
+    PE_TRY(pe_launch(attention_decode_kernel, grid, 32 * AD_WARPS, smem, s, 
         (const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row,
-        nh, nkv, window, scale * 1.4426950408889634f, split_len, n_splits, (float*)scratch, (bf16*)out);
+        nh, nkv, window, scale * 1.4426950408889634f, split_len, n_splits, (float*)scratch, (bf16*)out));
     PE_LAUNCH_CHECK();
     if (n_splits > 1) {
-        attention_decode_merge_kernel<<<T * nh, AD_HD < 64 ? 32 : (AD_HD <= 128 ? 64 : 128), 0, s>>>(
-            (const float*)scratch, n_splits, (bf16*)out);
+        PE_TRY(pe_launch(attention_decode_merge_kernel, T * nh, AD_HD < 64 ? 32 : (AD_HD <= 128 ? 64 : 128), 0, s, 
+            (const float*)scratch, n_splits, (bf16*)out));
         PE_LAUNCH_CHECK();
     }
     return 0;

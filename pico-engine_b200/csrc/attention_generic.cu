@@ -16,10 +16,12 @@
 
 template <typename T>
 __global__ void __launch_bounds__(AG_THREADS) attention_generic_kernel(
-    const T* __restrict__ q, int q_stride, T* __restrict__ out, const T* __restrict__ k_pool,
-    const T* __restrict__ v_pool, const int* __restrict__ block_table, int table_stride,
-    const int* __restrict__ tok_pos, const int* __restrict__ tok_row, int nh, int nkv, int hd, int window,
+    const T* q, int q_stride, T* out, const T* k_pool,
+    const T* v_pool, const int* block_table, int table_stride,
+    const int* tok_pos, const int* tok_row, int nh, int nkv, int hd, int window,
     float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float q_s[AG_MAX_HD];
     __shared__ float p_s[AG_THREADS];
     __shared__ long long base_s[AG_THREADS];
@@ -85,11 +87,11 @@ extern "C" int pe_attention_generic(const void* q, int q_stride, void* out, cons
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nh);
     if (dtype == PE_F32)
-        attention_generic_kernel<float><<<grid, AG_THREADS, 0, s>>>((const float*)q, q_stride, (float*)out,
-            (const float*)k_pool, (const float*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, hd, window, scale);
+        PE_TRY(pe_launch(attention_generic_kernel<float>, grid, AG_THREADS, 0, s, (const float*)q, q_stride, (float*)out,
+            (const float*)k_pool, (const float*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, hd, window, scale));
     else if (dtype == PE_BF16)
-        attention_generic_kernel<bf16><<<grid, AG_THREADS, 0, s>>>((const bf16*)q, q_stride, (bf16*)out,
-            (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, hd, window, scale);
+        PE_TRY(pe_launch(attention_generic_kernel<bf16>, grid, AG_THREADS, 0, s, (const bf16*)q, q_stride, (bf16*)out,
+            (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, hd, window, scale));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;

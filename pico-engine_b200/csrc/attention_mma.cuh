@@ -28,7 +28,13 @@ __device__ __forceinline__ unsigned am_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
 }
-__device__ __forceinline__ uint4 am_ld16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// Queries, keys and values were written by kernels that may still have been running when this
+// one started: they are read with plain coherent loads, never through the read-only path.
+__device__ __forceinline__ uint4 am_ld16(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 
 // Keys and values of one 16-key tile in registers: k[j][c] is the load of key j*8 + g,
 // v[h][c] the load of value row h*8 + g, each columns c*32 + t*8 .. +8.
@@ -38,8 +44,8 @@ struct AmTile {
 };
 
 // base: element offset of the tile's first key row in the pool (rows are AM_HD apart).
-__device__ __forceinline__ void am_load_tile(AmTile& tile, const bf16* __restrict__ k_pool,
-                                             const bf16* __restrict__ v_pool, size_t base, int g, int t) {
+__device__ __forceinline__ void am_load_tile(AmTile& tile, const bf16* k_pool,
+                                             const bf16* v_pool, size_t base, int g, int t) {
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int c = 0; c < AM_NCHUNK; ++c) {

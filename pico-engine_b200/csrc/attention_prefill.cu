@@ -20,9 +20,11 @@
 
 // tiles[i] = (batch row, first packed token, number of tokens (<= AP_QTILE), position of the first token)
 __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
-    const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, const bf16* __restrict__ k_pool,
-    const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int table_stride,
-    const int4* __restrict__ tiles, int nh, int nkv, int window, float scale_log2e) {
+    const bf16* q, int q_stride, bf16* out, const bf16* k_pool,
+    const bf16* v_pool, const int* block_table, int table_stride,
+    const int4* tiles, int nh, int nkv, int window, float scale_log2e) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int4 info = tiles[blockIdx.x];
     const int brow = info.x, tok0 = info.y, n = info.z, pos0 = info.w;
@@ -126,9 +128,9 @@ extern "C" int pe_attention_prefill(const void* q, int q_stride, void* out, cons
     if (hd != AM_HD || nkv <= 0 || nh % nkv || nh > 65535 || q_stride % 8) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out | (uintptr_t)tiles) & 15) return PE_ERR_UNSUPPORTED;
     dim3 grid(n_tiles, nh);
-    attention_prefill_kernel<<<grid, 32 * AP_WARPS, 0, (cudaStream_t)stream>>>(
+    PE_TRY(pe_launch(attention_prefill_kernel, grid, 32 * AP_WARPS, 0, (cudaStream_t)stream, 
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride,
-        (const int4*)tiles, nh, nkv, window, scale * 1.4426950408889634f);
+        (const int4*)tiles, nh, nkv, window, scale * 1.4426950408889634f));
     PE_LAUNCH_CHECK();
     return 0;
 }

@@ -116,6 +116,12 @@ def library_path(name: str, sources: Iterable[str], defines: Dict[str, str] | No
     tmp = f"{lib}.{os.getpid()}.tmp"
     _run([nvcc] + ARCH_FLAGS + ["-shared", "-o", tmp] + objs, f"linking {os.path.basename(lib)}")
     os.replace(tmp, lib)
+    for old in os.listdir(out_dir):                        # libraries of earlier versions of these sources
+        if old.startswith(f"libpico_{name}.") and old.endswith(".so") and os.path.join(out_dir, old) != lib:
+            try:
+                os.remove(os.path.join(out_dir, old))
+            except OSError:
+                pass
     for o in objs:
         try:
             os.remove(o)

@@ -18,6 +18,34 @@
 typedef __nv_bfloat16 bf16;
 
 #define PE_LAUNCH_CHECK() do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return (int)e_; } while (0)
+#define PE_TRY(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return (int)e_; } while (0)
+
+// Programmatic dependent launch.  Every kernel of this library is launched so that it may start
+// while its predecessor in the stream is still running (its blocks fill SMs the predecessor no
+// longer needs), and every kernel calls pdl_wait() before it touches anything an earlier kernel
+// wrote and before it writes anything: the wait returns when the predecessor has finished and
+// its writes are visible.  What a kernel does before the wait (reading weights, which no
+// kernel writes) overlaps the predecessor's tail.  pdl_launch_dependents() at a kernel's start
+// lets its own successor be scheduled as early as possible.  Because a kernel can be resident
+// while its predecessor still writes, kernel parameters are not declared __restrict__ (which
+// would let the compiler read them through the non-coherent path).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& pe_pdl_enabled() { static int on = 1; return on; }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t pe_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pe_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }

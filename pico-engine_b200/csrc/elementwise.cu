@@ -7,10 +7,15 @@
 // src/pico_engine/model.py:152 and the index_copy_ cache write at model.py:190-196.
 #include "common.cuh"
 
+// 1: kernels of this library may overlap their predecessor's tail (the default); 0: plain stream order.
+extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }
+
 // ---------------------------------------------------------------- embedding
 template <typename TW>
-__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+__global__ void embed_kernel(const TW* table, const int* ids, float* out,
                              int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);          // the host refuses such ids; never read outside the table
@@ -23,8 +28,8 @@ extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, floa
                         void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (table_dtype == PE_F32) embed_kernel<float><<<T, 256, 0, s>>>((const float*)table, ids, out, H, V);
-    else if (table_dtype == PE_BF16) embed_kernel<bf16><<<T, 256, 0, s>>>((const bf16*)table, ids, out, H, V);
+    if (table_dtype == PE_F32) PE_TRY(pe_launch(embed_kernel<float>, T, 256, 0, s, (const float*)table, ids, out, H, V));
+    else if (table_dtype == PE_BF16) PE_TRY(pe_launch(embed_kernel<bf16>, T, 256, 0, s, (const bf16*)table, ids, out, H, V));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
@@ -44,8 +49,10 @@ __device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float
 }
 
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
-                               const void* __restrict__ w, int w_dtype, float eps, TO* __restrict__ out, int H) {
+__global__ void rmsnorm_kernel(const float* x, const int* rows_index,
+                               const void* w, int w_dtype, float eps, TO* out, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows_index ? rows_index[r] : r) * H;
@@ -77,8 +84,8 @@ extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, 
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
-    if (out_dtype == PE_F32) rmsnorm_kernel<float><<<rows, threads, 0, s>>>(x, rows_index, w, w_dtype, eps, (float*)out, H);
-    else if (out_dtype == PE_BF16) rmsnorm_kernel<bf16><<<rows, threads, 0, s>>>(x, rows_index, w, w_dtype, eps, (bf16*)out, H);
+    if (out_dtype == PE_F32) PE_TRY(pe_launch(rmsnorm_kernel<float>, rows, threads, 0, s, x, rows_index, w, w_dtype, eps, (float*)out, H));
+    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(rmsnorm_kernel<bf16>, rows, threads, 0, s, x, rows_index, w, w_dtype, eps, (bf16*)out, H));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
@@ -89,7 +96,9 @@ extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const T* gu, T* out, int I, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
         out[idx] = from_f<T>(silu_mul(to_f(gu[t * 2 * I + i]), to_f(gu[t * 2 * I + I + i])));
@@ -97,7 +106,9 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 // I a multiple of 8: eight bfloat16 per thread with 16-byte loads and stores
-__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t groups) {
+__global__ void swiglu_bf16x8_kernel(const bf16* gu, bf16* out, int I, size_t groups) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int per_row = I / 8;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / per_row, i = (idx % per_row) * 8;
@@ -123,13 +134,13 @@ extern "C" int pe_swiglu(const void* gu, void* out, int dtype, int T, int I, voi
     if (dtype == PE_BF16 && I % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
         const size_t groups = total / 8;
         const int blocks = (int)((groups + 255) / 256 < 148 * 16 ? (groups + 255) / 256 : 148 * 16);
-        swiglu_bf16x8_kernel<<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, groups);
+        PE_TRY(pe_launch(swiglu_bf16x8_kernel, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, groups));
         PE_LAUNCH_CHECK();
         return 0;
     }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == PE_F32) swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, total);
-    else if (dtype == PE_BF16) swiglu_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
+    if (dtype == PE_F32) PE_TRY(pe_launch(swiglu_kernel<float>, blocks, 256, 0, s, (const float*)gu, (float*)out, I, total));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(swiglu_kernel<bf16>, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, total));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
@@ -138,7 +149,9 @@ extern "C" int pe_swiglu(const void* gu, void* out, int dtype, int T, int I, voi
 // ---------------------------------------------------------------- residual add
 // x[t, :] += y[t, :] in float32 (y in either dtype): the epilogue of a library matrix product.
 template <typename T>
-__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ y, size_t total) {
+__global__ void residual_add_kernel(float* x, const T* y, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         x[i] += to_f(y[i]);
 }
@@ -153,7 +166,9 @@ __device__ __forceinline__ float4 load4_as_f(const bf16* p) {
 
 // total a multiple of 4, both pointers aligned for 4-element accesses
 template <typename T>
-__global__ void residual_add_x4_kernel(float* __restrict__ x, const T* __restrict__ y, size_t groups) {
+__global__ void residual_add_x4_kernel(float* x, const T* y, size_t groups) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
         float4 a = *reinterpret_cast<float4*>(x + 4 * i);
         const float4 b = load4_as_f(y + 4 * i);
@@ -168,15 +183,15 @@ extern "C" int pe_residual_add(float* x, const void* y, int y_dtype, long long t
     if (total % 4 == 0 && !(((uintptr_t)x | (uintptr_t)y) & 15) && (y_dtype == PE_F32 || y_dtype == PE_BF16)) {
         const long long groups = total / 4, wantg = (groups + 255) / 256;
         const int blocksg = (int)(wantg < 148 * 16 ? wantg : 148 * 16);
-        if (y_dtype == PE_F32) residual_add_x4_kernel<float><<<blocksg, 256, 0, s>>>(x, (const float*)y, (size_t)groups);
-        else residual_add_x4_kernel<bf16><<<blocksg, 256, 0, s>>>(x, (const bf16*)y, (size_t)groups);
+        if (y_dtype == PE_F32) PE_TRY(pe_launch(residual_add_x4_kernel<float>, blocksg, 256, 0, s, x, (const float*)y, (size_t)groups));
+        else PE_TRY(pe_launch(residual_add_x4_kernel<bf16>, blocksg, 256, 0, s, x, (const bf16*)y, (size_t)groups));
         PE_LAUNCH_CHECK();
         return 0;
     }
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    if (y_dtype == PE_F32) residual_add_kernel<float><<<blocks, 256, 0, s>>>(x, (const float*)y, (size_t)total);
-    else if (y_dtype == PE_BF16) residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(x, (const bf16*)y, (size_t)total);
+    if (y_dtype == PE_F32) PE_TRY(pe_launch(residual_add_kernel<float>, blocks, 256, 0, s, x, (const float*)y, (size_t)total));
+    else if (y_dtype == PE_BF16) PE_TRY(pe_launch(residual_add_kernel<bf16>, blocks, 256, 0, s, x, (const bf16*)y, (size_t)total));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
@@ -184,7 +199,9 @@ extern "C" int pe_residual_add(float* x, const void* y, int y_dtype, long long t
 
 // ---------------------------------------------------------------- bias add (library matrix product epilogue)
 template <typename T>
-__global__ void bias_add_kernel(T* __restrict__ y, const void* __restrict__ bias, int bias_dtype, int N, size_t total) {
+__global__ void bias_add_kernel(T* y, const void* bias, int bias_dtype, int N, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         y[i] = from_f<T>(to_f(y[i]) + load_as_f(bias, bias_dtype, i % N));
 }
@@ -195,8 +212,8 @@ extern "C" int pe_bias_add(void* y, int dtype, const void* bias, int bias_dtype,
     const size_t total = (size_t)M * N;
     const size_t want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    if (dtype == PE_F32) bias_add_kernel<float><<<blocks, 256, 0, s>>>((float*)y, bias, bias_dtype, N, total);
-    else if (dtype == PE_BF16) bias_add_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)y, bias, bias_dtype, N, total);
+    if (dtype == PE_F32) PE_TRY(pe_launch(bias_add_kernel<float>, blocks, 256, 0, s, (float*)y, bias, bias_dtype, N, total));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(bias_add_kernel<bf16>, blocks, 256, 0, s, (bf16*)y, bias, bias_dtype, N, total));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
@@ -209,11 +226,13 @@ extern "C" int pe_bias_add(void* y, int dtype, const void* bias, int bias_dtype,
 // paged cache at (page of the token's sequence, position % PE_PAGE) when `store` is set.
 // Pool layout: [page][kv head][PE_PAGE][hd].
 template <typename T>
-__global__ void rope_store_kernel(T* __restrict__ qkv, int n_q, int n_kv, int hd,
-                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                  const int* __restrict__ tok_pos, const int* __restrict__ tok_row,
-                                  T* __restrict__ k_pool, T* __restrict__ v_pool,
-                                  const int* __restrict__ block_table, int table_stride, int store) {
+__global__ void rope_store_kernel(T* qkv, int n_q, int n_kv, int hd,
+                                  const float* cos_t, const float* sin_t,
+                                  const int* tok_pos, const int* tok_row,
+                                  T* k_pool, T* v_pool,
+                                  const int* block_table, int table_stride, int store) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const int half = hd >> 1;
@@ -257,11 +276,11 @@ extern "C" int pe_rope_store(void* qkv, int dtype, int T, int n_q, int n_kv, int
     if (hd % 2) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == PE_F32)
-        rope_store_kernel<float><<<T, 256, 0, s>>>((float*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
-                                                    (float*)k_pool, (float*)v_pool, block_table, table_stride, store);
+        PE_TRY(pe_launch(rope_store_kernel<float>, T, 256, 0, s, (float*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
+                                                    (float*)k_pool, (float*)v_pool, block_table, table_stride, store));
     else if (dtype == PE_BF16)
-        rope_store_kernel<bf16><<<T, 256, 0, s>>>((bf16*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
-                                                   (bf16*)k_pool, (bf16*)v_pool, block_table, table_stride, store);
+        PE_TRY(pe_launch(rope_store_kernel<bf16>, T, 256, 0, s, (bf16*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
+                                                   (bf16*)k_pool, (bf16*)v_pool, block_table, table_stride, store));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;

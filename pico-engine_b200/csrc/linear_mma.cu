@@ -32,6 +32,13 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
+// Activations were written by the preceding kernel: a plain (coherent) load, never the read-only path.
+__device__ __forceinline__ uint4 ld_act(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -49,9 +56,9 @@ __device__ __forceinline__ void lm_store(void* out, int epilogue, size_t o, floa
 // NT: number of 8-row tiles of A (M <= 8 * NT)
 template <int NT>
 __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
-    const bf16* __restrict__ A, const bf16* __restrict__ W, const void* __restrict__ bias, int bias_dtype,
-    void* __restrict__ out, int epilogue, int M, int N, int K, int splits, int k_per_split,
-    float* __restrict__ partial, unsigned int* __restrict__ tickets) {
+    const bf16* A, const bf16* W, const void* bias, int bias_dtype,
+    void* out, int epilogue, int M, int N, int K, int splits, int k_per_split,
+    float* partial, unsigned int* tickets) {
     __shared__ float red[LM_WARPS][NT * 4][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * LM_ROWS;
@@ -70,6 +77,8 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
     const bf16* w1 = W + (size_t)(ok1 ? r1 : 0) * K;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
+    pdl_launch_dependents();
+    bool waited = false;
     for (int base = warp; base < n_steps; base += LM_WARPS * LM_UNROLL) {
         uint4 wa[LM_UNROLL], wb[LM_UNROLL];
 #pragma unroll
@@ -79,6 +88,7 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
             wa[u] = (ok0 && kin) ? ldg_stream(w0 + k) : zero;
             wb[u] = (ok1 && kin) ? ldg_stream(w1 + k) : zero;
         }
+        if (!waited) { pdl_wait(); waited = true; }        // W is never written by a kernel; A is the predecessor's output
 #pragma unroll
         for (int u = 0; u < LM_UNROLL; ++u) {
             const int k = k_begin + (base + u * LM_WARPS) * 32 + t * 8;
@@ -86,12 +96,13 @@ __global__ void __launch_bounds__(32 * LM_WARPS) linear_mma_kernel(
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int m = j * 8 + g;
-                const uint4 a = (m < M && kin) ? __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * K + k)) : zero;
+                const uint4 a = (m < M && kin) ? ld_act(A + (size_t)m * K + k) : zero;
                 mma_bf16(acc[j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
                 mma_bf16(acc[j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
             }
         }
     }
+    if (!waited) pdl_wait();
 
     // acc[j][e] of lane (g, t): W row n0 + g + (e & 2 ? 8 : 0), A row j*8 + 2t + (e & 1)
 #pragma unroll
@@ -164,8 +175,8 @@ extern "C" int pe_linear_mma(const void* A, const void* W, const void* bias, int
     dim3 grid((N + LM_ROWS - 1) / LM_ROWS, splits);
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = (M + 7) / 8;
-#define LM_GO(NT) linear_mma_kernel<NT><<<grid, 32 * LM_WARPS, 0, s>>>((const bf16*)A, (const bf16*)W, bias, bias_dtype, out, \
-        epilogue, M, N, K, splits, k_per_split, (float*)partial, (unsigned int*)tickets)
+#define LM_GO(NT) PE_TRY(pe_launch(linear_mma_kernel<NT>, grid, 32 * LM_WARPS, 0, s, (const bf16*)A, (const bf16*)W, bias, bias_dtype, out, \
+        epilogue, M, N, K, splits, k_per_split, (float*)partial, (unsigned int*)tickets))
     switch (nt) {
         case 1: LM_GO(1); break;
         case 2: LM_GO(2); break;

@@ -15,9 +15,11 @@
 
 // epilogue: 0 store float32, 1 store bfloat16, 2 add into float32 (the residual stream)
 template <typename TA, typename TW>
-__global__ void __launch_bounds__(256) linear_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
-                                                          const void* __restrict__ bias, int bias_dtype,
-                                                          void* __restrict__ out, int epilogue, int M, int N, int K) {
+__global__ void __launch_bounds__(256) linear_simt_kernel(const TA* A, const TW* W,
+                                                          const void* bias, int bias_dtype,
+                                                          void* out, int epilogue, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[LS_BK][LS_BM + 4];
     __shared__ float Ws[LS_BK][LS_BN + 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -75,7 +77,7 @@ extern "C" int pe_linear_simt(const void* A, int a_dtype, const void* W, int w_d
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid((N + LS_BN - 1) / LS_BN, (M + LS_BM - 1) / LS_BM);
     if (grid.y > 65535) return PE_ERR_UNSUPPORTED;
-#define LS_GO(TA, TW) linear_simt_kernel<TA, TW><<<grid, 256, 0, s>>>((const TA*)A, (const TW*)W, bias, bias_dtype, out, epilogue, M, N, K)
+#define LS_GO(TA, TW) PE_TRY(pe_launch(linear_simt_kernel<TA, TW>, grid, 256, 0, s, (const TA*)A, (const TW*)W, bias, bias_dtype, out, epilogue, M, N, K))
     if (a_dtype == PE_F32 && w_dtype == PE_F32) LS_GO(float, float);
     else if (a_dtype == PE_BF16 && w_dtype == PE_BF16) LS_GO(bf16, bf16);
     else if (a_dtype == PE_BF16 && w_dtype == PE_F32) LS_GO(bf16, float);

@@ -80,8 +80,10 @@ __device__ __forceinline__ unsigned long long ax_block_max(unsigned long long v,
     return v;                                                 // valid in warp 0
 }
 
-__global__ void __launch_bounds__(AX_THREADS) argmax_partial_kernel(const float* __restrict__ logits, int V, int chunks,
-                                                                    unsigned long long* __restrict__ part) {
+__global__ void __launch_bounds__(AX_THREADS) argmax_partial_kernel(const float* logits, int V, int chunks,
+                                                                    unsigned long long* part) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ unsigned long long scratch[32];
     const int b = blockIdx.y, c = blockIdx.x;
     const float* row = logits + (size_t)b * V;
@@ -95,8 +97,10 @@ __global__ void __launch_bounds__(AX_THREADS) argmax_partial_kernel(const float*
     if (threadIdx.x == 0) part[(size_t)b * chunks + c] = best;
 }
 
-__global__ void __launch_bounds__(AX_THREADS) argmax_final_kernel(const unsigned long long* __restrict__ part, int chunks,
-                                                                  int* __restrict__ out) {
+__global__ void __launch_bounds__(AX_THREADS) argmax_final_kernel(const unsigned long long* part, int chunks,
+                                                                  int* out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ unsigned long long scratch[32];
     unsigned long long best = 0ull;
     for (int i = threadIdx.x; i < chunks; i += AX_THREADS) {
@@ -114,9 +118,9 @@ extern "C" int pe_argmax(const float* logits, int* out, int B, int V, void* scra
     if (V <= 0 || B > 65535 || !scratch) return PE_ERR_UNSUPPORTED;
     const int chunks = (V + AX_CHUNK - 1) / AX_CHUNK;
     cudaStream_t s = (cudaStream_t)stream;
-    argmax_partial_kernel<<<dim3(chunks, B), AX_THREADS, 0, s>>>(logits, V, chunks, (unsigned long long*)scratch);
+    PE_TRY(pe_launch(argmax_partial_kernel, dim3(chunks, B), AX_THREADS, 0, s, logits, V, chunks, (unsigned long long*)scratch));
     PE_LAUNCH_CHECK();
-    argmax_final_kernel<<<B, AX_THREADS, 0, s>>>((const unsigned long long*)scratch, chunks, out);
+    PE_TRY(pe_launch(argmax_final_kernel, B, AX_THREADS, 0, s, (const unsigned long long*)scratch, chunks, out));
     PE_LAUNCH_CHECK();
     return 0;
 }
@@ -137,10 +141,12 @@ extern "C" float pe_draw_uniform(unsigned long long seed, unsigned long long req
 }
 
 // ---------------------------------------------------------------- temperature / top-k / top-p sampling
-__global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V,
+__global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* logits, int* out, int V,
                                                             float temperature, int top_k, float top_p,
-                                                            unsigned long long seed, const int* __restrict__ request,
-                                                            const int* __restrict__ step) {
+                                                            unsigned long long seed, const int* request,
+                                                            const int* step) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float fscratch[33];
     __shared__ int iscratch[33];
     __shared__ double dscratch[33];
@@ -241,7 +247,7 @@ extern "C" int pe_sample(const float* logits, int* out, int B, int V, float temp
                          unsigned long long seed, const int* request, const int* step, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0 || !(temperature > 0.f)) return PE_ERR_UNSUPPORTED;
-    sample_kernel<<<B, SP_THREADS, 0, (cudaStream_t)stream>>>(logits, out, V, temperature, top_k, top_p, seed, request, step);
+    PE_TRY(pe_launch(sample_kernel, B, SP_THREADS, 0, (cudaStream_t)stream, logits, out, V, temperature, top_k, top_p, seed, request, step));
     PE_LAUNCH_CHECK();
     return 0;
 }

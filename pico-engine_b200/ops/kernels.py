@@ -317,3 +317,84 @@ def attention(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, hea
                                  table_stride, tiles, tok_pos.shape[0], window, scale)
     return attention_generic(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, table_stride,
                              tok_pos, tok_row, window, scale)
+
+
+# ---------------------------------------------------------------------------- fused decode products (bfloat16, up to 16 rows)
+
+FUSED_MAX_ROWS = 16
+
+
+def fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor) -> bool:
+    """Whether the fused decode kernels take a product with ``rows`` rows and weight ``w``."""
+    return (rows <= FUSED_MAX_ROWS and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.is_contiguous()
+            and w.data_ptr() % 16 == 0 and all(t.is_contiguous() and t.data_ptr() % 16 == 0 for t in others))
+
+
+def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
+                 norm_of: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                 eps: float = 0.0) -> torch.Tensor:
+    """a [M <= 16, K] . w [N, K]^T (+ bias); with ``norm_of`` (float32 [M, K]) the operand is
+    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``."""
+    src = norm_of if norm_of is not None else a
+    M, K = src.shape
+    N = w.shape[0]
+    _need(w, "w", torch.bfloat16, (N, K))
+    if norm_of is not None:
+        _need(norm_of, "norm_of", torch.float32); _need(norm_weight, "norm_weight", None, (K,))
+    else:
+        _need(a, "a", torch.bfloat16)
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    if accumulate_into is not None:
+        _need(accumulate_into, "accumulate_into", torch.float32, (M, N))
+        out, epilogue = accumulate_into, 2
+    else:
+        out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=w.device)
+        epilogue = _EPILOGUE_STORE[out.dtype]
+    check(core().pe_linear_fused(_ptr(a), _ptr(norm_of), _ptr(norm_weight),
+                                 0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
+                                 w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
+                                 epilogue, M, N, K, stream_ptr()), "linear_fused")
+    return out
+
+
+def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(h Wg^T) * (h Wu^T) with h = RMSNorm(x); x float32 [M <= 16, K], w_gate_up [2I, K] (gate rows first)."""
+    M, K = x.shape
+    I = w_gate_up.shape[0] // 2
+    _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
+    act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
+    check(core().pe_norm_gate_up_swiglu(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
+                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, stream_ptr()), "norm_gate_up_swiglu")
+    return act
+
+
+def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_qkv: torch.Tensor,
+                        b_qkv: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, cos: Optional[torch.Tensor],
+                        sin: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_row: torch.Tensor,
+                        k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                        block_table: Optional[torch.Tensor], table_stride: int) -> torch.Tensor:
+    """Rotated queries [M, n_q * head_dim] of h = RMSNorm(x); rotated keys and the values go to
+    the cache pages (skipped when ``k_pool`` is None)."""
+    M, K = x.shape
+    N = (n_q + 2 * n_kv) * head_dim
+    _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_qkv, "w_qkv", torch.bfloat16, (N, K))
+    if b_qkv is not None:
+        _need(b_qkv, "b_qkv", None, (N,))
+    _need(tok_pos, "tok_pos", torch.int32, (M,)); _need(tok_row, "tok_row", torch.int32, (M,))
+    if cos is not None:
+        _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32, cos.shape)
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+        _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim):
+            raise KernelError(f"cache pool must be [pages, {n_kv}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
+    q = torch.empty(M, n_q * head_dim, dtype=torch.bfloat16, device=x.device)
+    check(core().pe_norm_qkv_rope_store(None, x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"),
+                                        float(eps), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
+                                        q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
+                                        tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
+                                        1 if store else 0, stream_ptr()), "norm_qkv_rope_store")
+    return q

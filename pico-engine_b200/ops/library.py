@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
@@ -10,7 +11,8 @@ from ..csrc import build
 
 P, I, F, LL, ULL = c_void_p, c_int, c_float, c_longlong, c_ulonglong
 
-CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_mma.cu")
+CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_mma.cu",
+                "linear_fused.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -26,6 +28,9 @@ _SIGNATURES = {
     "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P],
     "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
     "pe_linear_mma_splits": [I, I],
+    "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P],
+    "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P],
+    "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P],
 }
 
 _HEAD_DIM_SIGNATURES = {
@@ -58,6 +63,7 @@ def core() -> ctypes.CDLL:
     if _core is None:
         lib = build.load("core", CORE_SOURCES)
         declare(lib, _SIGNATURES)
+        lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
         lib.pe_draw_uniform.argtypes = [ULL, ULL, ULL]
         lib.pe_draw_uniform.restype = c_float
         lib.pe_argmax_scratch_bytes.argtypes = [I, I]
@@ -81,6 +87,7 @@ def for_head_dim(head_dim: int) -> ctypes.CDLL:
     if lib is None:
         lib = build.load(f"attention_hd{head_dim}", HEAD_DIM_SOURCES, {"PE_HEAD_DIM": str(head_dim)})
         declare(lib, _HEAD_DIM_SIGNATURES)
+        lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
         lib.pe_attention_decode_scratch_bytes.argtypes = [I, I, I, I]
         lib.pe_attention_decode_scratch_bytes.restype = c_longlong
         _by_head_dim[head_dim] = lib

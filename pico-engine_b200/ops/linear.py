@@ -2,7 +2,8 @@
 kernel for a matrix product.
 
 * bfloat16 activations and weights, few rows (decoding): the tensor-core weight-streaming
-  kernel of ``csrc/linear_mma.cu`` with bias and residual in its epilogue.
+  kernels with bias and residual in their epilogue: ``csrc/linear_fused.cu`` up to 16 rows,
+  ``csrc/linear_mma.cu`` up to 64.
 * bfloat16, many rows (prompts): the library product (cuBLAS through ``torch.mm``), which is
   where pico-engine uses a library too (src/pico_engine/model.py:177, 213, 223, 235), followed
   by this library's bias or residual kernel.
@@ -24,6 +25,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         M = a.shape[0]
+        if kernels.fused_takes(M, w, a):
+            return kernels.linear_fused(a, w, bias, out_dtype, accumulate_into)
         if M <= SMALL_M and kernels.linear_mma_takes(a, w):
             return kernels.linear_mma(a, w, bias, out_dtype, accumulate_into)
         if bias is not None and bias.dtype == a.dtype:

@@ -78,6 +78,29 @@ class GQAAttention(Mixer):
     def apply(self, h, ctx, entry, cache_entry, owns_cache):
         return linear(self._attend(h, ctx, cache_entry, owns_cache), self.w_o, out_dtype=ctx.dtype)
 
+    def _fused(self, x, norm, ctx) -> bool:
+        """Decoding a few sequences in bfloat16: norm, projection, position encoding and cache
+        write are one kernel (csrc/linear_fused.cu)."""
+        from .norm import RMSNorm
+        from .position import NoPosition, RotaryHalf
+        return (ctx.dtype == torch.bfloat16 and type(norm) is RMSNorm and type(self.position) in (RotaryHalf, NoPosition)
+                and (self.b_qkv is None or self.b_qkv.dtype in (torch.bfloat16, torch.float32))
+                and kernels.fused_takes(x.shape[0], self.w_qkv, x) and kernels.fused_takes(x.shape[0], self.w_o))
+
     def add_to(self, x, norm, ctx, entry, cache_entry, owns_cache):
+        if self._fused(x, norm, ctx):
+            s = self.spec
+            kv = ctx.kv(cache_entry)
+            cos, sin = getattr(self.position, "cos", None), getattr(self.position, "sin", None)
+            if cos is not None and ctx.max_context > cos.shape[0]:
+                raise ValueError(f"a sequence reaches position {ctx.max_context - 1}, the rotary tables hold "
+                                 f"{cos.shape[0]} positions")
+            q = kernels.norm_qkv_rope_store(x, norm.weight, norm.eps, self.w_qkv, self.b_qkv, s.n_heads, s.n_kv_heads,
+                                            s.head_dim, cos, sin, ctx.tok_pos, ctx.tok_row,
+                                            kv.k if owns_cache else None, kv.v if owns_cache else None, kv.table, kv.stride)
+            a = kernels.attention(q, q.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table, kv.stride,
+                                  ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
+            kernels.linear_fused(a, self.w_o, accumulate_into=x)
+            return
         a = self._attend(norm.forward(x, ctx.dtype), ctx, cache_entry, owns_cache)
         linear(a, self.w_o, accumulate_into=x)

@@ -364,3 +364,81 @@ def test_sample_draws_do_not_depend_on_the_batch(K):
     for i in range(4):
         hist[i] = (draws == i).sum()
     assert torch.allclose(hist / 4000, torch.tensor([1, 2, 4, 1]) / 8.0, atol=0.03)
+
+
+# ---------------------------------------------------------------------------- fused decode products
+
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+@pytest.mark.parametrize("N,K_", [(100, 96), (896, 896), (896, 4864), (9728, 896), (70, 160), (5000, 3584)])
+def test_linear_fused(K, M, N, K_):
+    a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
+    want = a.double() @ w.double().T
+    A, W = dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16))
+    assert K.fused_takes(M, W, A)
+    got = K.linear_fused(A, W, out_dtype=torch.float32)
+    assert torch.allclose(got.cpu().double(), want, atol=1e-4, rtol=1e-4), float((got.cpu().double() - want).abs().max())
+    got = K.linear_fused(A, W, dev(b), out_dtype=torch.bfloat16)
+    assert torch.allclose(got.float().cpu().double(), want + b.double(), atol=4e-2, rtol=1e-2)
+    x = rnd(M, N, seed=4)
+    got = K.linear_fused(A, W, dev(b.to(torch.bfloat16)), accumulate_into=dev(x.clone()))
+    assert torch.allclose(got.cpu().double(), x.double() + want + b.double(), atol=1e-4, rtol=1e-4)
+    # the operand as the RMSNorm of float32 rows
+    xs, nw = rnd(M, K_, seed=5, scale=2.0), bf(1 + rnd(K_, seed=6) * 0.1)
+    h = plain.rms_norm(xs, nw, 1e-5).to(torch.bfloat16).double()
+    for nw_dtype in (torch.bfloat16, torch.float32):
+        got = K.linear_fused(None, W, out_dtype=torch.float32, norm_of=dev(xs), norm_weight=dev(nw.to(nw_dtype)), eps=1e-5)
+        assert torch.allclose(got.cpu().double(), h @ w.double().T, atol=3e-2, rtol=1e-2)   # a bfloat16 rounding of h may flip
+
+
+def test_linear_fused_rows_do_not_depend_on_their_neighbours(K):
+    a, w = bf(rnd(16, 4864, seed=1)), bf(rnd(896, 4864, seed=2, scale=0.02))
+    W = dev(w.to(torch.bfloat16))
+    whole = K.linear_fused(dev(a.to(torch.bfloat16)), W, out_dtype=torch.float32)
+    for rows in ([5], [0, 15], list(range(3, 12))):
+        assert torch.equal(K.linear_fused(dev(a[rows].to(torch.bfloat16)), W, out_dtype=torch.float32), whole[rows])
+
+
+@pytest.mark.parametrize("M,H,I", [(1, 64, 160), (8, 896, 4864), (16, 96, 352), (5, 3584, 1000)])
+def test_norm_gate_up_swiglu(K, M, H, I):
+    x, nw = rnd(M, H, seed=1, scale=2.0), bf(1 + rnd(H, seed=2) * 0.1)
+    w = bf(rnd(2 * I, H, seed=3, scale=H ** -0.5))
+    h = plain.rms_norm(x, nw, 1e-6).to(torch.bfloat16).float()
+    gu = (h @ w.T).to(torch.bfloat16).float()
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    got = K.norm_gate_up_swiglu(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)))
+    assert got.shape == (M, I) and torch.allclose(got.float().cpu(), want, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,H,theta,rotate", [(4, 2, 16, 64, 1e4, True), (3, 1, 32, 96, 1e6, True),
+                                                       (14, 2, 64, 896, 1e6, True), (5, 5, 48, 240, 1e4, False)])
+def test_norm_qkv_rope_store(K, nq, nkv, hd, H, theta, rotate):
+    lens, starts = [1] * 7, [62, 5, 63, 64, 0, 130, 17]           # seven sequences, one token each
+    M = len(lens)
+    x, nw = rnd(M, H, seed=1, scale=2.0), bf(1 + rnd(H, seed=2) * 0.1)
+    w, b = bf(rnd((nq + 2 * nkv) * hd, H, seed=3, scale=H ** -0.5)), bf(rnd((nq + 2 * nkv) * hd, seed=4, scale=0.3))
+    cos, sin = plain.rope_angles(torch.arange(200), hd, theta)
+    table = torch.arange(M * 3, dtype=torch.int32).flip(0).view(M, 3).contiguous()
+    kp = torch.zeros(M * 3, nkv, PAGE, hd, dtype=torch.bfloat16, device="cuda")
+    vp = torch.zeros_like(kp)
+    pos, row = torch.tensor(starts, dtype=torch.int32), torch.arange(M, dtype=torch.int32)
+    q = K.norm_qkv_rope_store(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)), dev(b.to(torch.bfloat16)),
+                              nq, nkv, hd, dev(cos) if rotate else None, dev(sin) if rotate else None, dev(pos), dev(row),
+                              kp, vp, dev(table), 3)
+    h = plain.rms_norm(x, nw, 1e-6).to(torch.bfloat16).float()
+    qkv = (h @ w.T + b).to(torch.bfloat16).float()
+    qk = qkv[:, :(nq + nkv) * hd].view(M, nq + nkv, hd)
+    if rotate:
+        qk = plain.apply_rope(qk, cos[pos.long()], sin[pos.long()])
+    v = qkv[:, (nq + nkv) * hd:].view(M, nkv, hd)
+    assert torch.allclose(q.float().cpu().view(M, nq, hd), qk[:, :nq], atol=4e-2, rtol=2e-2)
+    kc, vc = kp.float().cpu(), vp.float().cpu()
+    for m, p_ in enumerate(starts):
+        pg = int(table[m, p_ // PAGE])
+        assert torch.allclose(kc[pg, :, p_ % PAGE], qk[m, nq:], atol=4e-2, rtol=2e-2), m
+        assert torch.allclose(vc[pg, :, p_ % PAGE], v[m], atol=4e-2, rtol=2e-2), m
+    assert int((kc != 0).any(dim=-1).sum()) == M * nkv and int((vc != 0).any(dim=-1).sum()) == M * nkv
+    # without pools nothing is stored
+    kp.zero_()
+    K.norm_qkv_rope_store(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)), None, nq, nkv, hd,
+                          None, None, dev(pos), dev(row), None, None, dev(table), 3)
+    assert float(kp.abs().sum()) == 0.0
