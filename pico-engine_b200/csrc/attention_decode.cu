@@ -138,22 +138,41 @@ __global__ void __launch_bounds__(32 * AD_WARPS) attention_decode_kernel(
     }
 }
 
-// out[token][head][:] from the partials of all key ranges, added in the order of the ranges.
-__global__ void attention_decode_merge_kernel(const float* part, int n_splits, bf16* out) {
+// out[token][head][:] from the partials of all key ranges.  One block per (token, head); its
+// threads are AD_MERGE_GROUPS groups that each take every AD_MERGE_GROUPS-th range (so that the
+// loads of many ranges are in flight at once) and then add their sums in the order of the groups.
+#define AD_MERGE_GROUPS 4
+#define AD_MERGE_COLS (AD_HD < 32 ? 32 : AD_HD)
+
+__global__ void __launch_bounds__(AD_MERGE_GROUPS * AD_MERGE_COLS) attention_decode_merge_kernel(
+    const float* part, int n_splits, bf16* out) {
+    __shared__ float o_s[AD_MERGE_GROUPS][AD_MERGE_COLS], l_s[AD_MERGE_GROUPS], m_s[AD_MERGE_GROUPS];
     pdl_launch_dependents();
     pdl_wait();
     const size_t th = blockIdx.x;                          // token * nh + head
     const float* src = part + th * n_splits * AD_ROW;
+    const int col = threadIdx.x % AD_MERGE_COLS, grp = threadIdx.x / AD_MERGE_COLS;
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[(size_t)s * AD_ROW + AD_HD]);
-    for (int col = threadIdx.x; col < AD_HD; col += blockDim.x) {
-        float o = 0.f, l = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float* p = src + (size_t)s * AD_ROW;
-            const float wgt = (p[AD_HD] == -INFINITY) ? 0.f : exp2f(p[AD_HD] - m);
-            o = fmaf(p[col], wgt, o);
-            l = fmaf(p[AD_HD + 1], wgt, l);
-        }
+    for (int s = grp; s < n_splits; s += AD_MERGE_GROUPS) m = fmaxf(m, src[(size_t)s * AD_ROW + AD_HD]);
+    if (col == 0) m_s[grp] = m;
+    __syncthreads();
+    m = m_s[0];
+#pragma unroll
+    for (int w = 1; w < AD_MERGE_GROUPS; ++w) m = fmaxf(m, m_s[w]);
+    float o = 0.f, l = 0.f;
+#pragma unroll 4
+    for (int s = grp; s < n_splits; s += AD_MERGE_GROUPS) {
+        const float* p = src + (size_t)s * AD_ROW;
+        const float wgt = (p[AD_HD] == -INFINITY) ? 0.f : exp2f(p[AD_HD] - m);
+        if (col < AD_HD) o = fmaf(p[col], wgt, o);
+        l = fmaf(p[AD_HD + 1], wgt, l);
+    }
+    o_s[grp][col] = o;
+    if (col == 0) l_s[grp] = l;
+    __syncthreads();
+    if (grp == 0 && col < AD_HD) {
+#pragma unroll
+        for (int w = 1; w < AD_MERGE_GROUPS; ++w) { o += o_s[w][col]; l += l_s[w]; }
         out[th * AD_HD + col] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
 }
@@ -205,7 +224,7 @@ extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const
         nh, nkv, window, scale * 1.4426950408889634f, split_len, n_splits, (float*)scratch, (bf16*)out));
     PE_LAUNCH_CHECK();
     if (n_splits > 1) {
-        PE_TRY(pe_launch(attention_decode_merge_kernel, T * nh, AD_HD < 64 ? 32 : (AD_HD <= 128 ? 64 : 128), 0, s, 
+        PE_TRY(pe_launch(attention_decode_merge_kernel, T * nh, AD_MERGE_GROUPS * AD_MERGE_COLS, 0, s, 
             (const float*)scratch, n_splits, (bf16*)out));
         PE_LAUNCH_CHECK();
     }

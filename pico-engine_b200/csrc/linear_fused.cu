@@ -9,14 +9,22 @@
 //             ROPE      rows are query, key and value heads: add bias, rotate query and key heads
 //                       by position, write queries to out and keys and values into the paged cache
 //
-// At these sizes a product is bound by memory latency, not bandwidth: what counts is the number
-// of dependent trips to memory.  A CTA of eight warps owns 8 or 16 rows of W over all of K (no
-// split over CTAs, hence no second pass), its warps take the 32-wide k steps in turn, and every
-// warp issues the loads of four steps of W before it waits for the preceding kernel
-// (griddepcontrol.wait) and touches activations.  The roles of the MMA operands are swapped as
-// in linear_mma.cu: rows of W are the M side of mma.sync m16n8k16, sequences the N side.  The
-// 16 rows of a tile are two groups of 8: for SWIGLU the matching gate and up rows, for ROPE
-// the two halves of a head that rotate together, so the epilogue finds its pairs in one CTA.
+// At these sizes a product is bound by memory latency, not bandwidth: what counts is how many
+// bytes are in flight and how few dependent trips to memory a kernel makes.  A CTA of eight
+// warps owns 8 or 16 rows of W over all of K (no split over CTAs, hence no second pass).  Its
+// rows are brought into shared memory by bulk asynchronous copies (cp.async.bulk, the 1-D TMA
+// path, completing on an mbarrier), one copy per row and chunk of up to 1024 columns, up to
+// four chunks in flight; registers hold none of it, so many CTAs are resident and the whole
+// matrix can be under way at once.  The copies are issued before the kernel waits for its
+// predecessor (griddepcontrol.wait): no kernel writes weights.  The roles of the MMA operands
+// are swapped as in linear_mma.cu: rows of W are the M side of mma.sync m16n8k16, sequences
+// the N side; the warps take the 32-wide k steps of a chunk in turn and add their partial sums
+// in shared memory in the order of the warps.  The 16 rows of a tile are two groups of 8: for
+// SWIGLU the matching gate and up rows, for ROPE the two halves of a head that rotate
+// together, so the epilogue finds its pairs in one CTA.
+//
+// Waiting on an mbarrier is bounded: a wait that runs out sets *status to 1 and the CTA
+// returns, leaving its outputs unwritten; the host reads the status word with its results.
 //
 // pico-engine runs these as separate launches: rmsnorm, F.linear, rope, index_copy_, addmm,
 // silu_mul (src/pico_engine/model.py:175-235).
@@ -24,6 +32,10 @@
 
 #define LF_WARPS 8
 #define LF_UNROLL 4
+#define LF_MAX_CHUNK 1024            // columns of W per bulk copy
+#define LF_MAX_STAGES 4              // for 16-row tiles; 8-row tiles keep twice as many chunks in flight
+#define LF_ROW_PAD 8                 // bfloat16 of padding per row in shared memory: skews the banks
+#define LF_WAIT_CYCLES 2000000000ll    // about a second of SM clock: the longest a CTA waits for its own copies
 
 enum { LF_PLAIN = 0, LF_RMSNORM = 1 };
 enum { LF_STORE_F32 = 0, LF_STORE_BF16 = 1, LF_ACCUM = 2, LF_SWIGLU = 3, LF_ROPE = 4 };
@@ -38,6 +50,7 @@ struct LfArgs {
     void* out;                // STORE: [M, N]; ACCUM: float [M, N]; SWIGLU: bf16 [M, I]; ROPE: bf16 [M, n_q * hd]
     int M, N, K;
     int rows;                 // STORE/ACCUM: rows of W per CTA, 8 or 16
+    int chunk, stages;        // columns per bulk copy (a multiple of 32) and copies in flight per row
     int I;                    // SWIGLU
     // ROPE
     int n_q, n_kv, hd;
@@ -46,10 +59,32 @@ struct LfArgs {
     bf16* k_pool; bf16* v_pool; const int* block_table; int table_stride; int store;
 };
 
-__device__ __forceinline__ uint4 lf_ldg_stream(const void* p) {
+__device__ __forceinline__ unsigned lf_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lf_bar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void lf_bar_expect(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lf_bulk_copy(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// true when the phase with this parity has completed; false when the wait ran out
+__device__ __forceinline__ bool lf_bar_wait(unsigned bar, unsigned parity) {
+    const long long deadline = clock64() + LF_WAIT_CYCLES;
+    for (;;) {
+        unsigned done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (clock64() > deadline) return false;
+        __nanosleep(40);
+    }
+}
+__device__ __forceinline__ uint4 lf_lds16(unsigned addr) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint4 lf_ld16(const void* p) {       // coherent: data of the preceding kernel
@@ -70,42 +105,65 @@ __device__ __forceinline__ unsigned lf_pack(float lo, float hi) {
 
 // NT: 8-row tiles of sequences (M <= 8 * NT)
 template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(32 * LF_WARPS) linear_fused_kernel(const LfArgs p) {
+__global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_kernel(const LfArgs p, int* status) {
+    extern __shared__ __align__(128) unsigned char lf_smem[];   // [stage][16 rows][chunk + pad] bfloat16
+    __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES];
     __shared__ float red[LF_WARPS][NT * 4][32];
     __shared__ float ssq[LF_WARPS][NT * 8];
     __shared__ float rstd_s[NT * 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int K = p.K, M = p.M;
 
-    // which rows of W this lane streams: r_lo feeds MMA rows 0-7, r_hi rows 8-15
-    int r_lo, r_hi;
+    // the rows of W of this tile: group lo feeds MMA rows 0-7, group hi rows 8-15 (hi_base < 0: none)
+    int lo_base, hi_base;
     if (EPI == LF_SWIGLU) {
-        r_lo = blockIdx.x * 8 + g; r_hi = p.I + r_lo;
+        lo_base = blockIdx.x * 8; hi_base = p.I + lo_base;
     } else if (EPI == LF_ROPE) {
         const int half = p.hd >> 1, per_head = half >> 3;
-        r_lo = (blockIdx.x / per_head) * p.hd + (blockIdx.x % per_head) * 8 + g; r_hi = r_lo + half;
+        lo_base = (blockIdx.x / per_head) * p.hd + (blockIdx.x % per_head) * 8; hi_base = lo_base + half;
     } else {
-        r_lo = blockIdx.x * p.rows + g; r_hi = p.rows == 16 ? r_lo + 8 : p.N;
+        lo_base = blockIdx.x * p.rows; hi_base = p.rows == 16 ? lo_base + 8 : -1;
     }
-    const bool ok_lo = r_lo < p.N, ok_hi = r_hi < p.N;
-    const bf16* w_lo = p.W + (size_t)(ok_lo ? r_lo : 0) * K;
-    const bf16* w_hi = p.W + (size_t)(ok_hi ? r_hi : 0) * K;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    const int n_steps = (K + 31) / 32;
+    const int chunk = p.chunk, n_chunks = (K + chunk - 1) / chunk, stages = p.stages;
+    const int tile_rows = hi_base < 0 ? 8 : 16;              // rows of the tile held in shared memory
+    const unsigned row_bytes = (unsigned)(chunk + LF_ROW_PAD) * 2u, stage_bytes = (unsigned)tile_rows * row_bytes;
+    const unsigned smem0 = lf_smem_addr(lf_smem), bar0 = lf_smem_addr(bars);
 
-    float acc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    // row rr (0..15) of the tile in shared memory holds this row of W, or zeros
+    const int my_row = lane < 8 ? lo_base + lane : (hi_base < 0 ? -1 : hi_base + lane - 8);
+    const bool my_row_ok = lane < tile_rows && my_row >= 0 && my_row < p.N;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) lf_bar_init(bar0 + 8u * s, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1 && lane < tile_rows && !my_row_ok) {     // rows that no copy fills read as zeros
+        for (int s = 0; s < stages; ++s)
+            for (unsigned o = 0; o < row_bytes; o += 16)
+                *reinterpret_cast<uint4*>(lf_smem + s * stage_bytes + lane * row_bytes + o) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+
+    // chunk c of every valid row into stage c % stages; called by all of warp 0
+    auto issue = [&](int c) {
+        const int k0 = c * chunk, cols = min(chunk, K - k0);
+        const unsigned bar = bar0 + 8u * (c % stages);
+        const unsigned n_ok = __popc(__ballot_sync(0xffffffffu, my_row_ok));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of the stage precede its refill
+        if (lane == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
+        __syncwarp();
+        if (my_row_ok)
+            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + lane * row_bytes, p.W + (size_t)my_row * K + k0,
+                         (unsigned)cols * 2u, bar);
+    };
 
     pdl_launch_dependents();
-    uint4 wa[LF_UNROLL], wb[LF_UNROLL];
-#pragma unroll
-    for (int u = 0; u < LF_UNROLL; ++u) {                   // W first: no kernel writes it, so it need not wait
-        const int k = (warp + u * LF_WARPS) * 32 + t * 8;
-        wa[u] = (ok_lo && k < K) ? lf_ldg_stream(w_lo + k) : zero;
-        wb[u] = (ok_hi && k < K) ? lf_ldg_stream(w_hi + k) : zero;
-    }
-    pdl_wait();                                             // from here on the preceding kernel's results may be read
+    if (warp == 0)                                           // W first: no kernel writes it, so it need not wait
+        for (int c = 0; c < n_chunks && c < stages; ++c) issue(c);
+    pdl_wait();                                              // from here on the preceding kernel's results may be read
+
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const int n_steps = (K + 31) / 32;
     if (PRO == LF_RMSNORM) {
         // sum of squares of every row of x: each warp over the k steps it owns, then over the warps
         float part[NT];
@@ -139,38 +197,69 @@ __global__ void __launch_bounds__(32 * LF_WARPS) linear_fused_kernel(const LfArg
         }
         __syncthreads();
     }
-    for (int base = warp; base < n_steps; base += LF_WARPS * LF_UNROLL) {
-        if (base != warp) {
+
+    float acc[NT][4];
 #pragma unroll
-            for (int u = 0; u < LF_UNROLL; ++u) {
-                const int k = (base + u * LF_WARPS) * 32 + t * 8;
-                wa[u] = (ok_lo && k < K) ? lf_ldg_stream(w_lo + k) : zero;
-                wb[u] = (ok_hi && k < K) ? lf_ldg_stream(w_hi + k) : zero;
-            }
-        }
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    // the activations of this warp's steps of chunk c (a chunk has at most LF_WARPS * LF_UNROLL steps)
+    auto load_a = [&](int c, uint4 (&a)[LF_UNROLL][NT]) {
+        const int k0 = c * chunk, cols = min(chunk, K - k0);
 #pragma unroll
         for (int u = 0; u < LF_UNROLL; ++u) {
-            const int k = (base + u * LF_WARPS) * 32 + t * 8;
+            const int col = (warp + u * LF_WARPS) * 32 + t * 8, k = k0 + col;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int m = j * 8 + g;
-                uint4 a = zero;
-                if (m < M && k < K) {
+                a[u][j] = zero;
+                if (c < n_chunks && m < M && col < cols) {
                     if (PRO == LF_RMSNORM) {
                         const float4 x0 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k);
                         const float4 x1 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k + 4);
                         const float r = rstd_s[m];
-                        a.x = lf_pack(x0.x * r * load_as_f(p.norm_w, p.norm_w_dtype, k), x0.y * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 1));
-                        a.y = lf_pack(x0.z * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 2), x0.w * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 3));
-                        a.z = lf_pack(x1.x * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 4), x1.y * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 5));
-                        a.w = lf_pack(x1.z * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 6), x1.w * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 7));
+                        a[u][j].x = lf_pack(x0.x * r * load_as_f(p.norm_w, p.norm_w_dtype, k), x0.y * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 1));
+                        a[u][j].y = lf_pack(x0.z * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 2), x0.w * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 3));
+                        a[u][j].z = lf_pack(x1.x * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 4), x1.y * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 5));
+                        a[u][j].w = lf_pack(x1.z * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 6), x1.w * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 7));
                     } else {
-                        a = lf_ld16(p.A + (size_t)m * K + k);
+                        a[u][j] = lf_ld16(p.A + (size_t)m * K + k);
                     }
                 }
-                lf_mma(acc[j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
-                lf_mma(acc[j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
             }
+        }
+    };
+
+    uint4 a_cur[LF_UNROLL][NT], a_next[LF_UNROLL][NT];
+    load_a(0, a_cur);
+    for (int c = 0; c < n_chunks; ++c) {
+        const int k0 = c * chunk, cols = min(chunk, K - k0), steps = (cols + 31) / 32;
+        const unsigned stage = smem0 + (c % stages) * stage_bytes;
+        load_a(c + 1, a_next);                               // in flight while this chunk's W is awaited and used
+        if (warp < steps && !lf_bar_wait(bar0 + 8u * (c % stages), (unsigned)(c / stages) & 1u)) {
+            atomicExch(status, 1);                           // the copies did not arrive: give up, loudly
+            return;
+        }
+#pragma unroll
+        for (int u = 0; u < LF_UNROLL; ++u) {
+            const int step = warp + u * LF_WARPS, col = step * 32 + t * 8;
+            if (step < steps) {                              // the same for all lanes of the warp: the MMA needs them all
+                const bool in = col < cols;                  // a last step may be narrower than 32 columns
+                const uint4 wa = in ? lf_lds16(stage + g * row_bytes + col * 2) : zero;
+                const uint4 wb = (in && tile_rows == 16) ? lf_lds16(stage + (8 + g) * row_bytes + col * 2) : zero;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    lf_mma(acc[j], wa.x, wb.x, wa.y, wb.y, a_cur[u][j].x, a_cur[u][j].y);
+                    lf_mma(acc[j], wa.z, wb.z, wa.w, wb.w, a_cur[u][j].z, a_cur[u][j].w);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < LF_UNROLL; ++u)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) a_cur[u][j] = a_next[u][j];
+        if (c + stages < n_chunks) {                         // the stage is free again: refill it
+            __syncthreads();
+            if (warp == 0) issue(c + stages);
         }
     }
 
@@ -242,11 +331,28 @@ __global__ void __launch_bounds__(32 * LF_WARPS) linear_fused_kernel(const LfArg
     }
 }
 
-template <int PRO, int EPI>
-static int lf_launch(const LfArgs& a, int tiles, cudaStream_t s) {
-    if (a.M <= 8) PE_TRY(pe_launch(linear_fused_kernel<1, PRO, EPI>, tiles, 32 * LF_WARPS, 0, s, a));
-    else PE_TRY(pe_launch(linear_fused_kernel<2, PRO, EPI>, tiles, 32 * LF_WARPS, 0, s, a));
+template <int NT, int PRO, int EPI>
+static int lf_launch_nt(const LfArgs& a, int tiles, size_t smem, int* status, cudaStream_t s) {
+    static size_t allowed = 48 * 1024;                       // per instantiation: dynamic shared memory opted into
+    if (smem > allowed) {
+        PE_TRY(cudaFuncSetAttribute(linear_fused_kernel<NT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        allowed = smem;
+    }
+    PE_TRY(pe_launch(linear_fused_kernel<NT, PRO, EPI>, tiles, 32 * LF_WARPS, smem, s, a, status));
     return 0;
+}
+
+template <int PRO, int EPI>
+static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
+    if (!status) return PE_ERR_UNSUPPORTED;
+    a.chunk = a.K >= LF_MAX_CHUNK ? LF_MAX_CHUNK : (a.K + 31) / 32 * 32;
+    const int n_chunks = (a.K + a.chunk - 1) / a.chunk;
+    const int max_stages = (EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? LF_MAX_STAGES : 2 * LF_MAX_STAGES;
+    a.stages = n_chunks < max_stages ? n_chunks : max_stages;
+    const int tile_rows = (EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? 16 : 8;
+    const size_t smem = (size_t)a.stages * tile_rows * (a.chunk + LF_ROW_PAD) * 2;
+    if (a.M <= 8) return lf_launch_nt<1, PRO, EPI>(a, tiles, smem, status, s);
+    return lf_launch_nt<2, PRO, EPI>(a, tiles, smem, status, s);
 }
 
 static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }
@@ -256,35 +362,35 @@ static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 // epilogue: 0 store float32, 1 store bfloat16, 2 add into float32 out.
 extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* norm_w, int norm_w_dtype, float eps,
                                const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M, int N,
-                               int K, void* stream) {
+                               int K, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || epilogue < 0 || epilogue > 2 || !lf_aligned(W) || !lf_aligned(x_norm ? (const void*)x_norm : a))
         return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.A = (const bf16*)a; p.X = x_norm; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps;
     p.W = (const bf16*)W; p.bias = bias; p.bias_dtype = bias_dtype; p.out = out; p.M = M; p.N = N; p.K = K;
-    p.rows = (N + 15) / 16 >= 2 * 148 ? 16 : 8;              // small matrices: more, thinner CTAs
+    p.rows = (N + 15) / 16 >= 148 ? 16 : 8;                  // small matrices: more, thinner CTAs
     const int tiles = (N + p.rows - 1) / p.rows;
     cudaStream_t s = (cudaStream_t)stream;
     if (x_norm) {
-        if (epilogue == 0) return lf_launch<LF_RMSNORM, LF_STORE_F32>(p, tiles, s);
-        if (epilogue == 1) return lf_launch<LF_RMSNORM, LF_STORE_BF16>(p, tiles, s);
-        return lf_launch<LF_RMSNORM, LF_ACCUM>(p, tiles, s);
+        if (epilogue == 0) return lf_launch<LF_RMSNORM, LF_STORE_F32>(p, tiles, status, s);
+        if (epilogue == 1) return lf_launch<LF_RMSNORM, LF_STORE_BF16>(p, tiles, status, s);
+        return lf_launch<LF_RMSNORM, LF_ACCUM>(p, tiles, status, s);
     }
-    if (epilogue == 0) return lf_launch<LF_PLAIN, LF_STORE_F32>(p, tiles, s);
-    if (epilogue == 1) return lf_launch<LF_PLAIN, LF_STORE_BF16>(p, tiles, s);
-    return lf_launch<LF_PLAIN, LF_ACCUM>(p, tiles, s);
+    if (epilogue == 0) return lf_launch<LF_PLAIN, LF_STORE_F32>(p, tiles, status, s);
+    if (epilogue == 1) return lf_launch<LF_PLAIN, LF_STORE_BF16>(p, tiles, status, s);
+    return lf_launch<LF_PLAIN, LF_ACCUM>(p, tiles, status, s);
 }
 
 // act[M, I] = silu(h . Wg^T) * (h . Wu^T), h = RMSNorm(x); W = [Wg; Wu] is [2I, K].
 extern "C" int pe_norm_gate_up_swiglu(const float* x, const void* norm_w, int norm_w_dtype, float eps, const void* W,
-                                      void* act, int M, int I, int K, void* stream) {
+                                      void* act, int M, int I, int K, int* status, void* stream) {
     if (M <= 0 || I <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || I % 8 || !lf_aligned(W) || !lf_aligned(x)) return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.X = x; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps; p.W = (const bf16*)W; p.out = act;
     p.M = M; p.N = 2 * I; p.K = K; p.I = I; p.rows = 16;
-    return lf_launch<LF_RMSNORM, LF_SWIGLU>(p, I / 8, (cudaStream_t)stream);
+    return lf_launch<LF_RMSNORM, LF_SWIGLU>(p, I / 8, status, (cudaStream_t)stream);
 }
 
 // q[M, n_q * hd] and the cache pages of keys and values from h = RMSNorm(x) (or from bfloat16
@@ -294,7 +400,7 @@ extern "C" int pe_norm_qkv_rope_store(const void* a, const float* x, const void*
                                       const void* W, const void* bias, int bias_dtype, void* q_out, int M, int K,
                                       int n_q, int n_kv, int hd, const float* cos_t, const float* sin_t,
                                       const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
-                                      const int* block_table, int table_stride, int store, void* stream) {
+                                      const int* block_table, int table_stride, int store, int* status, void* stream) {
     if (M <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || hd % 16 || !lf_aligned(W) || !lf_aligned(x ? (const void*)x : a)) return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
@@ -304,6 +410,6 @@ extern "C" int pe_norm_qkv_rope_store(const void* a, const float* x, const void*
     p.tok_row = tok_row; p.k_pool = (bf16*)k_pool; p.v_pool = (bf16*)v_pool; p.block_table = block_table;
     p.table_stride = table_stride; p.store = store;
     const int tiles = (n_q + 2 * n_kv) * (hd / 16);
-    if (x) return lf_launch<LF_RMSNORM, LF_ROPE>(p, tiles, (cudaStream_t)stream);
-    return lf_launch<LF_PLAIN, LF_ROPE>(p, tiles, (cudaStream_t)stream);
+    if (x) return lf_launch<LF_RMSNORM, LF_ROPE>(p, tiles, status, (cudaStream_t)stream);
+    return lf_launch<LF_PLAIN, LF_ROPE>(p, tiles, status, (cudaStream_t)stream);
 }

@@ -15,6 +15,7 @@ import torch
 
 from ..cache import Cache, PAGE
 from ..config.registry import architecture, read_config
+from ..ops import kernels
 from ..ops.library import core, require_cuda
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_folder, load_into, random_tensor
@@ -120,7 +121,9 @@ class Engine:
         self.last_timing = {"prefill_s": 0.0, "decode_s": 0.0, "decode_steps": 0, "h2d_bytes": 0}
         backend = EngineBackend(self, Sampler(params), use_graph)
         budget = self.cache.n_pages * PAGE if self.cache is not None else PAGE
-        return run_generation(backend, prompts, mnt, stop, self.max_batch, budget)
+        requests = run_generation(backend, prompts, mnt, stop, self.max_batch, budget)
+        kernels.check_status(self.device)
+        return requests
 
 
 class EngineBackend:

@@ -324,6 +324,21 @@ def attention(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, hea
 FUSED_MAX_ROWS = 16
 
 
+def status_word(device) -> torch.Tensor:
+    """The int32 word in which a kernel records that a bounded wait of its own ran out (0: none did)."""
+    from .workspace import scratch
+    return scratch("status", 4, torch.device(device), zeroed=True)[:4].view(torch.int32)
+
+
+def check_status(device) -> None:
+    """Raise if a kernel gave up waiting for its own copies since the last check.  Synchronises."""
+    word = status_word(device)
+    code = int(word.item())
+    if code:
+        word.zero_()
+        raise KernelError(f"a kernel gave up a bounded wait (status {code}); its results are incomplete")
+
+
 def fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor) -> bool:
     """Whether the fused decode kernels take a product with ``rows`` rows and weight ``w``."""
     return (rows <= FUSED_MAX_ROWS and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.is_contiguous()
@@ -355,7 +370,7 @@ def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torc
     check(core().pe_linear_fused(_ptr(a), _ptr(norm_of), _ptr(norm_weight),
                                  0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
                                  w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
-                                 epilogue, M, N, K, stream_ptr()), "linear_fused")
+                                 epilogue, M, N, K, status_word(w.device).data_ptr(), stream_ptr()), "linear_fused")
     return out
 
 
@@ -366,7 +381,8 @@ def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
     _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
     act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
     check(core().pe_norm_gate_up_swiglu(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
-                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, stream_ptr()), "norm_gate_up_swiglu")
+                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_word(x.device).data_ptr(),
+                                        stream_ptr()), "norm_gate_up_swiglu")
     return act
 
 
@@ -396,5 +412,5 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
                                         float(eps), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
                                         q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
                                         tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
-                                        1 if store else 0, stream_ptr()), "norm_qkv_rope_store")
+                                        1 if store else 0, status_word(x.device).data_ptr(), stream_ptr()), "norm_qkv_rope_store")
     return q
