@@ -191,3 +191,50 @@ extern "C" int pe_linear_mma(const void* A, const void* W, const void* bias, int
     PE_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------- the same product without any allocation
+// See linear_mma_static.h.  The scratch of the split ranges lives in this file-scope device
+// array.  Its name is a device symbol: host code may not pass `static_scratch` itself to a
+// kernel (on the host it is only a stand-in for the symbol), so the device address is looked
+// up once per device with cudaGetSymbolAddress and that pointer is what the kernel gets.
+#include "linear_mma_static.h"
+#include <mutex>
+
+static __device__ __align__(256) unsigned char static_scratch[PE_STATIC_SCRATCH_BYTES + PE_STATIC_TICKETS * sizeof(unsigned int)];
+
+#define PE_STATIC_MAX_DEVICES 64
+static void* static_scratch_address[PE_STATIC_MAX_DEVICES];     // device address of static_scratch, per device
+static std::mutex static_scratch_mutex;
+
+// The device address of the array on the current device; looked up on the first call there.
+static int static_scratch_on_current_device(void** address) {
+    int device = -1;
+    PE_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= PE_STATIC_MAX_DEVICES) return PE_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(static_scratch_mutex);
+    if (!static_scratch_address[device]) {
+        void* p = nullptr;
+        PE_TRY(cudaGetSymbolAddress(&p, static_scratch));       // with `device` current: its copy of the array
+        static_scratch_address[device] = p;
+    }
+    *address = static_scratch_address[device];
+    return 0;
+}
+
+extern "C" int pe_linear_mma_static(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int epilogue,
+                                    int M, int N, int K, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > LM_MAX_M || K <= 0 || K % 8 || epilogue < 0 || epilogue > 2) return PE_ERR_UNSUPPORTED;
+    const int splits = pe_linear_mma_splits(N, K);
+    const long long partial_bytes = pe_linear_mma_scratch_bytes(M, N, K);
+    const long long tickets = splits > 1 ? (N + LM_ROWS - 1) / LM_ROWS : 0;
+    if (partial_bytes > (long long)PE_STATIC_SCRATCH_BYTES || tickets > (long long)PE_STATIC_TICKETS)
+        return PE_ERR_STATIC_TOO_LARGE;
+    void* base = nullptr;
+    const int rc = static_scratch_on_current_device(&base);
+    if (rc) return rc;
+    unsigned char* ticket_area = (unsigned char*)base + PE_STATIC_SCRATCH_BYTES;
+    if (tickets)                                                 // whatever an earlier call left: tickets start at zero
+        PE_TRY(cudaMemsetAsync(ticket_area, 0, (size_t)tickets * sizeof(unsigned int), (cudaStream_t)stream));
+    return pe_linear_mma(A, W, bias, bias_dtype, out, epilogue, M, N, K, base, ticket_area, stream);
+}
