@@ -2,7 +2,8 @@
 // stands before and after it in the layer, so that a layer is five kernels instead of ten:
 //
 //   prologue  PLAIN     A is bfloat16 [M, K]
-//             RMSNORM   A = bfloat16(x * rsqrt(mean(x^2) + eps) * w) from the float32 residual stream x
+//             RMSNORM   A = RMSNorm(x) of the float32 residual stream x: bfloat16(x * w) is multiplied and
+//                       rsqrt(mean(x^2) + eps) applied to the sums, so x is read once
 //   epilogue  STORE     out[M, N] = acc (+ bias), bfloat16 or float32
 //             ACCUM     x[M, N] += acc (+ bias) in float32 (the residual sum)
 //             SWIGLU    out[M, I] = silu(gate) * up, gate and up being rows i and I + i of W
@@ -110,7 +111,6 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES];
     __shared__ float red[LF_WARPS][NT * 4][32];
     __shared__ float ssq[LF_WARPS][NT * 8];
-    __shared__ float rstd_s[NT * 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int K = p.K, M = p.M;
 
@@ -163,40 +163,11 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     pdl_wait();                                              // from here on the preceding kernel's results may be read
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    const int n_steps = (K + 31) / 32;
-    if (PRO == LF_RMSNORM) {
-        // sum of squares of every row of x: each warp over the k steps it owns, then over the warps
-        float part[NT];
+    // RMSNORM: the operand is bfloat16(x * w); the row's 1/rms is applied to the sums at the end (the
+    // product is linear in it), so x is read once and its squares are summed on the way
+    float ssq_part[NT];
 #pragma unroll
-        for (int j = 0; j < NT; ++j) part[j] = 0.f;
-        for (int b2 = warp; b2 < n_steps; b2 += LF_WARPS) {
-            const int k = b2 * 32 + t * 8;
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const int m = j * 8 + g;
-                if (m < M && k < K) {
-                    const float4 x0 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k);
-                    const float4 x1 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k + 4);
-                    part[j] += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w +
-                               x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            part[j] += __shfl_xor_sync(0xffffffffu, part[j], 1);
-            part[j] += __shfl_xor_sync(0xffffffffu, part[j], 2);
-            if (t == 0) ssq[warp][j * 8 + g] = part[j];
-        }
-        __syncthreads();
-        if (threadIdx.x < NT * 8) {
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < LF_WARPS; ++w) sum += ssq[w][threadIdx.x];
-            rstd_s[threadIdx.x] = 1.0f / sqrtf(sum / (float)K + p.eps);
-        }
-        __syncthreads();
-    }
+    for (int j = 0; j < NT; ++j) ssq_part[j] = 0.f;
 
     float acc[NT][4];
 #pragma unroll
@@ -216,11 +187,23 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                     if (PRO == LF_RMSNORM) {
                         const float4 x0 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k);
                         const float4 x1 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k + 4);
-                        const float r = rstd_s[m];
-                        a[u][j].x = lf_pack(x0.x * r * load_as_f(p.norm_w, p.norm_w_dtype, k), x0.y * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 1));
-                        a[u][j].y = lf_pack(x0.z * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 2), x0.w * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 3));
-                        a[u][j].z = lf_pack(x1.x * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 4), x1.y * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 5));
-                        a[u][j].w = lf_pack(x1.z * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 6), x1.w * r * load_as_f(p.norm_w, p.norm_w_dtype, k + 7));
+                        ssq_part[j] += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w +
+                                       x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+                        float w8[8];
+                        if (p.norm_w_dtype == PE_BF16) {
+                            const uint4 wv = *reinterpret_cast<const uint4*>((const bf16*)p.norm_w + k);
+                            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(w2[e]); w8[2 * e] = f.x; w8[2 * e + 1] = f.y; }
+                        } else {
+                            const float4 w0 = *reinterpret_cast<const float4*>((const float*)p.norm_w + k);
+                            const float4 w1 = *reinterpret_cast<const float4*>((const float*)p.norm_w + k + 4);
+                            w8[0] = w0.x; w8[1] = w0.y; w8[2] = w0.z; w8[3] = w0.w; w8[4] = w1.x; w8[5] = w1.y; w8[6] = w1.z; w8[7] = w1.w;
+                        }
+                        a[u][j].x = lf_pack(x0.x * w8[0], x0.y * w8[1]);
+                        a[u][j].y = lf_pack(x0.z * w8[2], x0.w * w8[3]);
+                        a[u][j].z = lf_pack(x1.x * w8[4], x1.y * w8[5]);
+                        a[u][j].w = lf_pack(x1.z * w8[6], x1.w * w8[7]);
                     } else {
                         a[u][j] = lf_ld16(p.A + (size_t)m * K + k);
                     }
@@ -268,6 +251,15 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) red[warp][j * 4 + e][lane] = acc[j][e];
+    if (PRO == LF_RMSNORM) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {                       // lanes (g, 0..3) hold parts of row j*8 + g
+            float v = ssq_part[j];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (t == 0) ssq[warp][j * 8 + g] = v;
+        }
+    }
     __syncthreads();
 
     // one thread per (sequence, row of the tile's first group); it sums both groups over the warps
@@ -278,6 +270,13 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
         float v_lo = 0.f, v_hi = 0.f;
 #pragma unroll
         for (int w = 0; w < LF_WARPS; ++w) { v_lo += red[w][j * 4 + e1][ln]; v_hi += red[w][j * 4 + 2 + e1][ln]; }
+        if (PRO == LF_RMSNORM) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < LF_WARPS; ++w) sum += ssq[w][m];
+            const float rstd = 1.0f / sqrtf(sum / (float)K + p.eps);
+            v_lo *= rstd; v_hi *= rstd;
+        }
 
         if (EPI == LF_SWIGLU) {
             const int i = blockIdx.x * 8 + r;

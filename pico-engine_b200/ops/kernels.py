@@ -265,18 +265,20 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
     return out
 
 
-PREFILL_TILE = 64
+PREFILL_TILE = 64     # AP_QTILE of csrc/attention_prefill.cu
 
 
 def prefill_tiles(lens, starts, device) -> torch.Tensor:
     """int32 [tiles, 4] = (batch row, first packed token, tokens, position of the first token):
-    the packed tokens of a step cut into runs of at most 64 tokens of one sequence."""
+    the packed tokens of a step cut into runs of at most 64 tokens of one sequence, the runs that
+    see the most keys first (they take longest, so they are scheduled first)."""
     rows = []
     tok = 0
     for b, (n, st) in enumerate(zip(lens, starts)):
         for off in range(0, n, PREFILL_TILE):
             rows.append((b, tok + off, min(PREFILL_TILE, n - off), st + off))
         tok += n
+    rows.sort(key=lambda r: -(r[3] + r[2]))
     return torch.tensor(rows, dtype=torch.int32).to(device, non_blocking=True)
 
 
