@@ -90,11 +90,23 @@ class ClockSampler:
         return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
-def reference_arm() -> int:
-    """pico-engine itself cannot be run for this metric here; say why in one line."""
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "pico-engine loads only GGUF checkpoints with an embedded tokenizer (none is on this machine and "
-                      "there is no network), runs one sequence at a time and has no random-weights mode"}))
+def reference_arm(steps: int, warmup: int, layers) -> int:
+    """pico-engine itself from baseline/_ref (see baseline/reference_arm.py), in a process of its own with a time
+    limit; whatever goes wrong there becomes the ``unavailable`` line."""
+    import subprocess
+    cmd = [sys.executable, os.path.join(ROOT, "baseline", "reference_arm.py"), "--steps", str(steps), "--warmup", str(warmup)]
+    if layers:
+        cmd += ["--layers", str(layers)]
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+        lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+        if proc.returncode == 0 and lines:
+            print(lines[-1])
+            return 0
+        why = (proc.stderr.strip().splitlines() or ["no output"])[-1][:300]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference run ended with code {proc.returncode}: {why}"}))
+    except subprocess.TimeoutExpired:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference run did not finish within 1500 s"}))
     return 0
 
 
@@ -107,7 +119,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (recorded in config)")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args.steps, max(args.warmup, 3), args.layers)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
