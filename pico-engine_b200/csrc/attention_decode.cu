@@ -184,7 +184,7 @@ extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }
 // only, never of the sequences' lengths (the same launch is replayed as sequences grow).
 extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_context, int* split_len_out) {
     const int G = nh / nkv, ctas = T * nkv * ((G + 15) / 16);
-    int want = (4 * 148 + ctas - 1) / ctas;
+    int want = 148 * (AD_HD <= 64 ? 3 : 2) / ctas;            // one wave: what is resident at once (registers allow 3 or 2 CTAs an SM)
     const int most = (max_context + PE_PAGE - 1) / PE_PAGE;
     if (want > most) want = most;
     if (want > 64) want = 64;

@@ -34,7 +34,7 @@
 #define LF_WARPS 8
 #define LF_UNROLL 4
 #define LF_MAX_CHUNK 1024            // columns of W per bulk copy
-#define LF_MAX_STAGES 4              // for 16-row tiles; 8-row tiles keep twice as many chunks in flight
+#define LF_MAX_STAGES 4              // chunks in flight: as many as fit in 160 KB of shared memory, at most twice this
 #define LF_ROW_PAD 8                 // bfloat16 of padding per row in shared memory: skews the banks
 #define LF_WAIT_CYCLES 2000000000ll    // about a second of SM clock: the longest a CTA waits for its own copies
 
@@ -58,6 +58,8 @@ struct LfArgs {
     const float* cos_t; const float* sin_t;
     const int* tok_pos; const int* tok_row;
     bf16* k_pool; bf16* v_pool; const int* block_table; int table_stride; int store;
+    // a hint: bring these bytes (the weights of the kernel that follows) towards L2 while this kernel runs
+    const unsigned char* ahead; long long ahead_bytes;
 };
 
 __device__ __forceinline__ unsigned lf_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -108,7 +110,7 @@ __device__ __forceinline__ unsigned lf_pack(float lo, float hi) {
 template <int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_kernel(const LfArgs p, int* status) {
     extern __shared__ __align__(128) unsigned char lf_smem[];   // [stage][16 rows][chunk + pad] bfloat16
-    __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES], bars_a[2 * LF_MAX_STAGES];
     __shared__ float red[LF_WARPS][NT * 4][32];
     __shared__ float ssq[LF_WARPS][NT * 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -126,21 +128,28 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     }
     const int chunk = p.chunk, n_chunks = (K + chunk - 1) / chunk, stages = p.stages;
     const int tile_rows = hi_base < 0 ? 8 : 16;              // rows of the tile held in shared memory
-    const unsigned row_bytes = (unsigned)(chunk + LF_ROW_PAD) * 2u, stage_bytes = (unsigned)tile_rows * row_bytes;
-    const unsigned smem0 = lf_smem_addr(lf_smem), bar0 = lf_smem_addr(bars);
+    const int a_rows = PRO == LF_PLAIN ? NT * 8 : 0;         // PLAIN: the activations of a chunk are staged beside W
+    const unsigned row_bytes = (unsigned)(chunk + LF_ROW_PAD) * 2u, stage_bytes = (unsigned)(tile_rows + a_rows) * row_bytes;
+    const unsigned smem0 = lf_smem_addr(lf_smem), bar0 = lf_smem_addr(bars), bar_a0 = lf_smem_addr(bars_a);
 
     // row rr (0..15) of the tile in shared memory holds this row of W, or zeros
     const int my_row = lane < 8 ? lo_base + lane : (hi_base < 0 ? -1 : hi_base + lane - 8);
     const bool my_row_ok = lane < tile_rows && my_row >= 0 && my_row < p.N;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) lf_bar_init(bar0 + 8u * s, 1u);
+        for (int s = 0; s < stages; ++s) { lf_bar_init(bar0 + 8u * s, 1u); lf_bar_init(bar_a0 + 8u * s, 1u); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1 && lane < tile_rows && !my_row_ok) {     // rows that no copy fills read as zeros
         for (int s = 0; s < stages; ++s)
             for (unsigned o = 0; o < row_bytes; o += 16)
                 *reinterpret_cast<uint4*>(lf_smem + s * stage_bytes + lane * row_bytes + o) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    const bool my_a_ok = lane < a_rows && lane < M;          // warp 1: lane m copies row m of A
+    if (warp == 2 && lane < a_rows && !my_a_ok) {
+        for (int s = 0; s < stages; ++s)
+            for (unsigned o = 0; o < row_bytes; o += 16)
+                *reinterpret_cast<uint4*>(lf_smem + s * stage_bytes + (tile_rows + lane) * row_bytes + o) = make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();
 
@@ -157,10 +166,34 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                          (unsigned)cols * 2u, bar);
     };
 
+    // the same for the activations (PLAIN only); called by all of warp 1, after the wait for the predecessor
+    auto issue_a = [&](int c) {
+        const int k0 = c * chunk, cols = min(chunk, K - k0);
+        const unsigned bar = bar_a0 + 8u * (c % stages);
+        const unsigned n_ok = __popc(__ballot_sync(0xffffffffu, my_a_ok));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (lane == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
+        __syncwarp();
+        if (my_a_ok)
+            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + (tile_rows + lane) * row_bytes, p.A + (size_t)lane * K + k0,
+                         (unsigned)cols * 2u, bar);
+    };
+
     pdl_launch_dependents();
     if (warp == 0)                                           // W first: no kernel writes it, so it need not wait
         for (int c = 0; c < n_chunks && c < stages; ++c) issue(c);
+    if (warp == 1 && p.ahead_bytes > 0) {                    // the following kernel's weights: each CTA asks for its share
+        const long long piece = 16384;
+        const long long pieces = (p.ahead_bytes + piece - 1) / piece;
+        for (long long i = (long long)blockIdx.x * 32 + lane; i < pieces; i += (long long)gridDim.x * 32) {
+            const long long off = i * piece;
+            const unsigned n = (unsigned)((p.ahead_bytes - off < piece ? p.ahead_bytes - off : piece) & ~15ll);
+            if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ahead + off), "r"(n) : "memory");
+        }
+    }
     pdl_wait();                                              // from here on the preceding kernel's results may be read
+    if (PRO == LF_PLAIN && warp == 1)
+        for (int c = 0; c < n_chunks && c < stages; ++c) issue_a(c);
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     // RMSNORM: the operand is bfloat16(x * w); the row's 1/rms is applied to the sums at the end (the
@@ -213,12 +246,14 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     };
 
     uint4 a_cur[LF_UNROLL][NT], a_next[LF_UNROLL][NT];
-    load_a(0, a_cur);
+    if (PRO == LF_RMSNORM) load_a(0, a_cur);
     for (int c = 0; c < n_chunks; ++c) {
         const int k0 = c * chunk, cols = min(chunk, K - k0), steps = (cols + 31) / 32;
         const unsigned stage = smem0 + (c % stages) * stage_bytes;
-        load_a(c + 1, a_next);                               // in flight while this chunk's W is awaited and used
-        if (warp < steps && !lf_bar_wait(bar0 + 8u * (c % stages), (unsigned)(c / stages) & 1u)) {
+        if (PRO == LF_RMSNORM) load_a(c + 1, a_next);        // in flight while this chunk's W is awaited and used
+        const unsigned parity = (unsigned)(c / stages) & 1u;
+        if (warp < steps && !(lf_bar_wait(bar0 + 8u * (c % stages), parity) &&
+                              (PRO != LF_PLAIN || lf_bar_wait(bar_a0 + 8u * (c % stages), parity)))) {
             atomicExch(status, 1);                           // the copies did not arrive: give up, loudly
             return;
         }
@@ -231,18 +266,23 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                 const uint4 wb = (in && tile_rows == 16) ? lf_lds16(stage + (8 + g) * row_bytes + col * 2) : zero;
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    lf_mma(acc[j], wa.x, wb.x, wa.y, wb.y, a_cur[u][j].x, a_cur[u][j].y);
-                    lf_mma(acc[j], wa.z, wb.z, wa.w, wb.w, a_cur[u][j].z, a_cur[u][j].w);
+                    const uint4 a = PRO == LF_PLAIN ? (in ? lf_lds16(stage + (tile_rows + j * 8 + g) * row_bytes + col * 2) : zero)
+                                                    : a_cur[u][j];
+                    lf_mma(acc[j], wa.x, wb.x, wa.y, wb.y, a.x, a.y);
+                    lf_mma(acc[j], wa.z, wb.z, wa.w, wb.w, a.z, a.w);
                 }
             }
         }
+        if (PRO == LF_RMSNORM) {
 #pragma unroll
-        for (int u = 0; u < LF_UNROLL; ++u)
+            for (int u = 0; u < LF_UNROLL; ++u)
 #pragma unroll
-            for (int j = 0; j < NT; ++j) a_cur[u][j] = a_next[u][j];
+                for (int j = 0; j < NT; ++j) a_cur[u][j] = a_next[u][j];
+        }
         if (c + stages < n_chunks) {                         // the stage is free again: refill it
             __syncthreads();
             if (warp == 0) issue(c + stages);
+            if (PRO == LF_PLAIN && warp == 1) issue_a(c + stages);
         }
     }
 
@@ -332,8 +372,8 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
 
 template <int NT, int PRO, int EPI>
 static int lf_launch_nt(const LfArgs& a, int tiles, size_t smem, int* status, cudaStream_t s) {
-    static size_t allowed = 48 * 1024;                       // per instantiation: dynamic shared memory opted into
-    if (smem > allowed) {
+    static size_t allowed = 36 * 1024;                       // per instantiation: dynamic shared memory opted into (the
+    if (smem > allowed) {                                    // kernel's static arrays take up to 9 KB of the default 48 KB)
         PE_TRY(cudaFuncSetAttribute(linear_fused_kernel<NT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         allowed = smem;
     }
@@ -346,11 +386,15 @@ static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
     if (!status) return PE_ERR_UNSUPPORTED;
     a.chunk = a.K >= LF_MAX_CHUNK ? LF_MAX_CHUNK : (a.K + 31) / 32 * 32;
     const int n_chunks = (a.K + a.chunk - 1) / a.chunk;
-    const int max_stages = (EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? LF_MAX_STAGES : 2 * LF_MAX_STAGES;
-    a.stages = n_chunks < max_stages ? n_chunks : max_stages;
+    const int nt = a.M <= 8 ? 1 : 2;
     const int tile_rows = (EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? 16 : 8;
-    const size_t smem = (size_t)a.stages * tile_rows * (a.chunk + LF_ROW_PAD) * 2;
-    if (a.M <= 8) return lf_launch_nt<1, PRO, EPI>(a, tiles, smem, status, s);
+    const size_t stage = (size_t)(tile_rows + (PRO == LF_PLAIN ? nt * 8 : 0)) * (a.chunk + LF_ROW_PAD) * 2;
+    int max_stages = (int)((160u << 10) / stage);            // chunks in flight: what fits in 160 KB, at most 8
+    if (max_stages > 2 * LF_MAX_STAGES) max_stages = 2 * LF_MAX_STAGES;
+    if (max_stages < 1) max_stages = 1;
+    a.stages = n_chunks < max_stages ? n_chunks : max_stages;
+    const size_t smem = (size_t)a.stages * stage;
+    if (nt == 1) return lf_launch_nt<1, PRO, EPI>(a, tiles, smem, status, s);
     return lf_launch_nt<2, PRO, EPI>(a, tiles, smem, status, s);
 }
 
@@ -361,13 +405,14 @@ static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 // epilogue: 0 store float32, 1 store bfloat16, 2 add into float32 out.
 extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* norm_w, int norm_w_dtype, float eps,
                                const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M, int N,
-                               int K, int* status, void* stream) {
+                               int K, const void* ahead, long long ahead_bytes, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || epilogue < 0 || epilogue > 2 || !lf_aligned(W) || !lf_aligned(x_norm ? (const void*)x_norm : a))
         return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.A = (const bf16*)a; p.X = x_norm; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps;
     p.W = (const bf16*)W; p.bias = bias; p.bias_dtype = bias_dtype; p.out = out; p.M = M; p.N = N; p.K = K;
+    p.ahead = (const unsigned char*)ahead; p.ahead_bytes = (ahead && !((uintptr_t)ahead & 15)) ? ahead_bytes : 0;
     p.rows = (N + 15) / 16 >= 148 ? 16 : 8;                  // small matrices: more, thinner CTAs
     const int tiles = (N + p.rows - 1) / p.rows;
     cudaStream_t s = (cudaStream_t)stream;
@@ -383,12 +428,14 @@ extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* n
 
 // act[M, I] = silu(h . Wg^T) * (h . Wu^T), h = RMSNorm(x); W = [Wg; Wu] is [2I, K].
 extern "C" int pe_norm_gate_up_swiglu(const float* x, const void* norm_w, int norm_w_dtype, float eps, const void* W,
-                                      void* act, int M, int I, int K, int* status, void* stream) {
+                                      void* act, int M, int I, int K, const void* ahead, long long ahead_bytes, int* status,
+                                      void* stream) {
     if (M <= 0 || I <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || I % 8 || !lf_aligned(W) || !lf_aligned(x)) return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.X = x; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps; p.W = (const bf16*)W; p.out = act;
     p.M = M; p.N = 2 * I; p.K = K; p.I = I; p.rows = 16;
+    p.ahead = (const unsigned char*)ahead; p.ahead_bytes = (ahead && !((uintptr_t)ahead & 15)) ? ahead_bytes : 0;
     return lf_launch<LF_RMSNORM, LF_SWIGLU>(p, I / 8, status, (cudaStream_t)stream);
 }
 
@@ -399,7 +446,8 @@ extern "C" int pe_norm_qkv_rope_store(const void* a, const float* x, const void*
                                       const void* W, const void* bias, int bias_dtype, void* q_out, int M, int K,
                                       int n_q, int n_kv, int hd, const float* cos_t, const float* sin_t,
                                       const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
-                                      const int* block_table, int table_stride, int store, int* status, void* stream) {
+                                      const int* block_table, int table_stride, int store, const void* ahead,
+                                      long long ahead_bytes, int* status, void* stream) {
     if (M <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || hd % 16 || !lf_aligned(W) || !lf_aligned(x ? (const void*)x : a)) return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
@@ -408,6 +456,7 @@ extern "C" int pe_norm_qkv_rope_store(const void* a, const float* x, const void*
     p.K = K; p.rows = 16; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.cos_t = cos_t; p.sin_t = sin_t; p.tok_pos = tok_pos;
     p.tok_row = tok_row; p.k_pool = (bf16*)k_pool; p.v_pool = (bf16*)v_pool; p.block_table = block_table;
     p.table_stride = table_stride; p.store = store;
+    p.ahead = (const unsigned char*)ahead; p.ahead_bytes = (ahead && !((uintptr_t)ahead & 15)) ? ahead_bytes : 0;
     const int tiles = (n_q + 2 * n_kv) * (hd / 16);
     if (x) return lf_launch<LF_RMSNORM, LF_ROPE>(p, tiles, status, (cudaStream_t)stream);
     return lf_launch<LF_PLAIN, LF_ROPE>(p, tiles, status, (cudaStream_t)stream);

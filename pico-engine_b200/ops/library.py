@@ -28,9 +28,9 @@ _SIGNATURES = {
     "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P],
     "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
     "pe_linear_mma_splits": [I, I],
-    "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
-    "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
-    "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
+    "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, LL, P, P],
+    "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, LL, P, P],
+    "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, LL, P, P],
 }
 
 _HEAD_DIM_SIGNATURES = {
