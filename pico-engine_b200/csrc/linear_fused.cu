@@ -58,8 +58,6 @@ struct LfArgs {
     const float* cos_t; const float* sin_t;
     const int* tok_pos; const int* tok_row;
     bf16* k_pool; bf16* v_pool; const int* block_table; int table_stride; int store;
-    // a hint: bring these bytes (the weights of the kernel that follows) towards L2 while this kernel runs
-    const unsigned char* ahead; long long ahead_bytes;
 };
 
 __device__ __forceinline__ unsigned lf_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -182,15 +180,6 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     pdl_launch_dependents();
     if (warp == 0)                                           // W first: no kernel writes it, so it need not wait
         for (int c = 0; c < n_chunks && c < stages; ++c) issue(c);
-    if (warp == 1 && p.ahead_bytes > 0) {                    // the following kernel's weights: each CTA asks for its share
-        const long long piece = 16384;
-        const long long pieces = (p.ahead_bytes + piece - 1) / piece;
-        for (long long i = (long long)blockIdx.x * 32 + lane; i < pieces; i += (long long)gridDim.x * 32) {
-            const long long off = i * piece;
-            const unsigned n = (unsigned)((p.ahead_bytes - off < piece ? p.ahead_bytes - off : piece) & ~15ll);
-            if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ahead + off), "r"(n) : "memory");
-        }
-    }
     pdl_wait();                                              // from here on the preceding kernel's results may be read
     if (PRO == LF_PLAIN && warp == 1)
         for (int c = 0; c < n_chunks && c < stages; ++c) issue_a(c);
@@ -405,14 +394,13 @@ static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 // epilogue: 0 store float32, 1 store bfloat16, 2 add into float32 out.
 extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* norm_w, int norm_w_dtype, float eps,
                                const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M, int N,
-                               int K, const void* ahead, long long ahead_bytes, int* status, void* stream) {
+                               int K, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || epilogue < 0 || epilogue > 2 || !lf_aligned(W) || !lf_aligned(x_norm ? (const void*)x_norm : a))
         return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.A = (const bf16*)a; p.X = x_norm; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps;
     p.W = (const bf16*)W; p.bias = bias; p.bias_dtype = bias_dtype; p.out = out; p.M = M; p.N = N; p.K = K;
-    p.ahead = (const unsigned char*)ahead; p.ahead_bytes = (ahead && !((uintptr_t)ahead & 15)) ? ahead_bytes : 0;
     p.rows = (N + 15) / 16 >= 148 ? 16 : 8;                  // small matrices: more, thinner CTAs
     const int tiles = (N + p.rows - 1) / p.rows;
     cudaStream_t s = (cudaStream_t)stream;
@@ -428,14 +416,12 @@ extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* n
 
 // act[M, I] = silu(h . Wg^T) * (h . Wu^T), h = RMSNorm(x); W = [Wg; Wu] is [2I, K].
 extern "C" int pe_norm_gate_up_swiglu(const float* x, const void* norm_w, int norm_w_dtype, float eps, const void* W,
-                                      void* act, int M, int I, int K, const void* ahead, long long ahead_bytes, int* status,
-                                      void* stream) {
+                                      void* act, int M, int I, int K, int* status, void* stream) {
     if (M <= 0 || I <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || I % 8 || !lf_aligned(W) || !lf_aligned(x)) return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.X = x; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps; p.W = (const bf16*)W; p.out = act;
     p.M = M; p.N = 2 * I; p.K = K; p.I = I; p.rows = 16;
-    p.ahead = (const unsigned char*)ahead; p.ahead_bytes = (ahead && !((uintptr_t)ahead & 15)) ? ahead_bytes : 0;
     return lf_launch<LF_RMSNORM, LF_SWIGLU>(p, I / 8, status, (cudaStream_t)stream);
 }
 
@@ -446,8 +432,7 @@ extern "C" int pe_norm_qkv_rope_store(const void* a, const float* x, const void*
                                       const void* W, const void* bias, int bias_dtype, void* q_out, int M, int K,
                                       int n_q, int n_kv, int hd, const float* cos_t, const float* sin_t,
                                       const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
-                                      const int* block_table, int table_stride, int store, const void* ahead,
-                                      long long ahead_bytes, int* status, void* stream) {
+                                      const int* block_table, int table_stride, int store, int* status, void* stream) {
     if (M <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || hd % 16 || !lf_aligned(W) || !lf_aligned(x ? (const void*)x : a)) return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
@@ -456,7 +441,6 @@ extern "C" int pe_norm_qkv_rope_store(const void* a, const float* x, const void*
     p.K = K; p.rows = 16; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.cos_t = cos_t; p.sin_t = sin_t; p.tok_pos = tok_pos;
     p.tok_row = tok_row; p.k_pool = (bf16*)k_pool; p.v_pool = (bf16*)v_pool; p.block_table = block_table;
     p.table_stride = table_stride; p.store = store;
-    p.ahead = (const unsigned char*)ahead; p.ahead_bytes = (ahead && !((uintptr_t)ahead & 15)) ? ahead_bytes : 0;
     const int tiles = (n_q + 2 * n_kv) * (hd / 16);
     if (x) return lf_launch<LF_RMSNORM, LF_ROPE>(p, tiles, status, (cudaStream_t)stream);
     return lf_launch<LF_PLAIN, LF_ROPE>(p, tiles, status, (cudaStream_t)stream);

@@ -350,10 +350,9 @@ def fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor) -> bool:
 def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
                  norm_of: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
-                 eps: float = 0.0, ahead: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 eps: float = 0.0) -> torch.Tensor:
     """a [M <= 16, K] . w [N, K]^T (+ bias); with ``norm_of`` (float32 [M, K]) the operand is
-    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``.  ``ahead``: a tensor (the next
-    kernel's weights) that the kernel asks the memory system to bring towards L2 meanwhile."""
+    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``."""
     src = norm_of if norm_of is not None else a
     M, K = src.shape
     N = w.shape[0]
@@ -373,25 +372,18 @@ def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torc
     check(core().pe_linear_fused(_ptr(a), _ptr(norm_of), _ptr(norm_weight),
                                  0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
                                  w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
-                                 epilogue, M, N, K, _ptr(ahead), _nbytes(ahead), status_word(w.device).data_ptr(),
-                                 stream_ptr()), "linear_fused")
+                                 epilogue, M, N, K, status_word(w.device).data_ptr(), stream_ptr()), "linear_fused")
     return out
 
 
-def _nbytes(t: Optional[torch.Tensor]) -> int:
-    return 0 if t is None else t.numel() * t.element_size()
-
-
-def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_gate_up: torch.Tensor,
-                        ahead: Optional[torch.Tensor] = None) -> torch.Tensor:
+def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(h Wg^T) * (h Wu^T) with h = RMSNorm(x); x float32 [M <= 16, K], w_gate_up [2I, K] (gate rows first)."""
     M, K = x.shape
     I = w_gate_up.shape[0] // 2
     _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
     act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
     check(core().pe_norm_gate_up_swiglu(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
-                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, _ptr(ahead), _nbytes(ahead),
-                                        status_word(x.device).data_ptr(),
+                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_word(x.device).data_ptr(),
                                         stream_ptr()), "norm_gate_up_swiglu")
     return act
 
@@ -400,8 +392,7 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
                         b_qkv: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, cos: Optional[torch.Tensor],
                         sin: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_row: torch.Tensor,
                         k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
-                        block_table: Optional[torch.Tensor], table_stride: int,
-                        ahead: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        block_table: Optional[torch.Tensor], table_stride: int) -> torch.Tensor:
     """Rotated queries [M, n_q * head_dim] of h = RMSNorm(x); rotated keys and the values go to
     the cache pages (skipped when ``k_pool`` is None)."""
     M, K = x.shape
@@ -423,6 +414,35 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
                                         float(eps), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
                                         q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
                                         tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
-                                        1 if store else 0, _ptr(ahead), _nbytes(ahead), status_word(x.device).data_ptr(),
-                                        stream_ptr()), "norm_qkv_rope_store")
+                                        1 if store else 0, status_word(x.device).data_ptr(), stream_ptr()), "norm_qkv_rope_store")
     return q
+
+
+# ---------------------------------------------------------------------------- tcgen05 products for many rows (bfloat16)
+
+def gemm_tcgen05_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
+            and a.is_contiguous() and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 accumulate_into: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+    """a [M, K] . w [N, K]^T on the tcgen05 tensor cores with a fused epilogue: bfloat16 result
+    (+ bias); or added into the float32 tensor ``accumulate_into``; or, with ``swiglu`` and
+    w = [gate rows; up rows], silu(gate) * up as bfloat16 [M, N / 2]."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a, "a", torch.bfloat16); _need(w, "w", torch.bfloat16, (N, K))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    if accumulate_into is not None:
+        _need(accumulate_into, "accumulate_into", torch.float32, (M, N))
+        out, epilogue = accumulate_into, 1
+    elif swiglu:
+        out, epilogue = torch.empty(M, N // 2, dtype=torch.bfloat16, device=a.device), 2
+    else:
+        out, epilogue = torch.empty(M, N, dtype=torch.bfloat16, device=a.device), 0
+    check(core().pe_gemm_tcgen05(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
+                                 out.data_ptr(), epilogue, M, N, K, status_word(a.device).data_ptr(), stream_ptr()),
+          "gemm_tcgen05")
+    return out

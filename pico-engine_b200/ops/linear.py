@@ -6,7 +6,8 @@ kernel for a matrix product.
   ``csrc/linear_mma.cu`` up to 64.
 * bfloat16, many rows (prompts): the library product (cuBLAS through ``torch.mm``), which is
   where pico-engine uses a library too (src/pico_engine/model.py:177, 213, 223, 235), followed
-  by this library's bias or residual kernel.
+  by this library's bias or residual kernel; or, where that is faster, the tcgen05 kernel of
+  ``csrc/gemm_tcgen05.cu`` with the residual sum in its epilogue.
 * anything else (the float32 engine; weights that were stored in float32): float32
   multiply-adds on the CUDA cores, ``csrc/linear_simt.cu``.
 """
@@ -19,6 +20,11 @@ import torch
 from . import kernels
 
 SMALL_M = 64        # up to this many rows the weight-streaming kernel is used
+# A product with a small weight that ends in the residual sum runs on this library's tcgen05 kernel,
+# which adds into the stream in its epilogue: there the library's product plus a separate pass over the
+# result costs more (17 us against 30 us for 2048 x 896 x 896).  Larger products are still faster in cuBLAS.
+TCGEN05_MAX_WEIGHT = 1 << 20
+TCGEN05_MAX_ROWS = 4096
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -29,6 +35,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             return kernels.linear_fused(a, w, bias, out_dtype, accumulate_into)
         if M <= SMALL_M and kernels.linear_mma_takes(a, w):
             return kernels.linear_mma(a, w, bias, out_dtype, accumulate_into)
+        if (accumulate_into is not None and bias is None and w.numel() <= TCGEN05_MAX_WEIGHT and M <= TCGEN05_MAX_ROWS
+                and kernels.gemm_tcgen05_takes(a, w)):
+            return kernels.gemm_tcgen05(a, w, accumulate_into=accumulate_into)
         if bias is not None and bias.dtype == a.dtype:
             y = torch.addmm(bias, a, w.t())                  # the library adds the bias in its epilogue
         else:

@@ -442,3 +442,34 @@ def test_norm_qkv_rope_store(K, nq, nkv, hd, H, theta, rotate):
     K.norm_qkv_rope_store(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)), None, nq, nkv, hd,
                           None, None, dev(pos), dev(row), None, None, dev(table), 3)
     assert float(kp.abs().sum()) == 0.0
+
+
+# ---------------------------------------------------------------------------- tcgen05 products for many rows
+
+@pytest.mark.parametrize("M", [65, 128, 300, 2048])
+@pytest.mark.parametrize("N,K_", [(1152, 896), (896, 896), (896, 4864), (136, 72), (3584, 3584)])
+def test_gemm_tcgen05(K, M, N, K_):
+    a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
+    A, W = dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16))
+    assert K.gemm_tcgen05_takes(A, W)
+    want = a.double() @ w.double().T
+    got = K.gemm_tcgen05(A, W, dev(b.to(torch.bfloat16)))
+    K.check_status("cuda")
+    err = (got.float().cpu().double() - (want + b.double())).abs()
+    assert got.shape == (M, N) and float(err.max()) < 4e-2, (float(err.max()), divmod(int(err.argmax()), N))
+    x = rnd(M, N, seed=4)
+    got = K.gemm_tcgen05(A, W, accumulate_into=dev(x.clone()))
+    K.check_status("cuda")
+    err = (got.cpu().double() - (x.double() + want)).abs()
+    assert float(err.max()) < 1e-3, (float(err.max()), divmod(int(err.argmax()), N))
+
+
+@pytest.mark.parametrize("M,H,I", [(70, 64, 160), (2048, 896, 4864), (129, 96, 352), (200, 3584, 1000)])
+def test_gemm_tcgen05_swiglu(K, M, H, I):
+    a, w = bf(rnd(M, H, seed=1)), bf(rnd(2 * I, H, seed=3, scale=H ** -0.5))
+    gu = (a @ w.T).to(torch.bfloat16).float()
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    got = K.gemm_tcgen05(dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16)), swiglu=True)
+    K.check_status("cuda")
+    err = (got.float().cpu() - want).abs()
+    assert got.shape == (M, I) and float(err.max()) < 4e-2, (float(err.max()), divmod(int(err.argmax()), I))
