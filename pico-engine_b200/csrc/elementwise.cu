@@ -269,6 +269,60 @@ __global__ void rope_store_kernel(T* qkv, int n_q, int n_kv, int hd,
     }
 }
 
+// The same for bfloat16 with head sizes that are multiples of 16: eight elements per thread, 16-byte accesses.
+__global__ void rope_store_bf16x8_kernel(bf16* qkv, int n_q, int n_kv, int hd, const float* cos_t, const float* sin_t,
+                                         const int* tok_pos, const int* tok_row, bf16* k_pool, bf16* v_pool,
+                                         const int* block_table, int table_stride, int store) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = hd >> 1, groups = half >> 3;               // groups of 8 pairs per head
+    bf16* row = qkv + (size_t)t * (n_q + 2 * n_kv) * hd;
+    size_t cache_base = 0;
+    bool do_store = false;
+    if (store) {
+        const int page = block_table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+        do_store = page >= 0;
+        cache_base = (size_t)page * n_kv * PE_PAGE * hd + (size_t)(pos % PE_PAGE) * hd;
+    }
+    for (int idx = threadIdx.x; idx < (n_q + n_kv) * groups; idx += blockDim.x) {
+        const int head = idx / groups, j = (idx % groups) * 8;
+        bf16* p = row + (size_t)head * hd;
+        uint4 lo = *reinterpret_cast<const uint4*>(p + j), hi = *reinterpret_cast<const uint4*>(p + j + half);
+        if (cos_t) {
+            const float* cp = cos_t + (size_t)pos * half + j;
+            const float* sp = sin_t + (size_t)pos * half + j;
+            const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(l2[e]), b = __bfloat1622float2(h2[e]);
+                l2[e] = __floats2bfloat162_rn(a.x * c[2 * e] - b.x * sn[2 * e], a.y * c[2 * e + 1] - b.y * sn[2 * e + 1]);
+                h2[e] = __floats2bfloat162_rn(a.x * sn[2 * e] + b.x * c[2 * e], a.y * sn[2 * e + 1] + b.y * c[2 * e + 1]);
+            }
+            *reinterpret_cast<uint4*>(p + j) = lo;
+            *reinterpret_cast<uint4*>(p + j + half) = hi;
+        }
+        if (do_store && head >= n_q) {
+            bf16* dst = k_pool + cache_base + (size_t)(head - n_q) * PE_PAGE * hd;
+            *reinterpret_cast<uint4*>(dst + j) = lo;
+            *reinterpret_cast<uint4*>(dst + j + half) = hi;
+        }
+    }
+    if (do_store) {
+        const bf16* v = row + (size_t)(n_q + n_kv) * hd;
+        for (int idx = threadIdx.x; idx < n_kv * hd / 8; idx += blockDim.x) {
+            const int head = (idx * 8) / hd, d = (idx * 8) % hd;
+            *reinterpret_cast<uint4*>(v_pool + cache_base + (size_t)head * PE_PAGE * hd + d) = *reinterpret_cast<const uint4*>(v + idx * 8);
+        }
+    }
+}
+
 extern "C" int pe_rope_store(void* qkv, int dtype, int T, int n_q, int n_kv, int hd, const float* cos_t,
                              const float* sin_t, const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
                              const int* block_table, int table_stride, int store, void* stream) {
@@ -278,6 +332,9 @@ extern "C" int pe_rope_store(void* qkv, int dtype, int T, int n_q, int n_kv, int
     if (dtype == PE_F32)
         PE_TRY(pe_launch(rope_store_kernel<float>, T, 256, 0, s, (float*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
                                                     (float*)k_pool, (float*)v_pool, block_table, table_stride, store));
+    else if (dtype == PE_BF16 && hd % 16 == 0 && !(((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15))
+        PE_TRY(pe_launch(rope_store_bf16x8_kernel, T, 128, 0, s, (bf16*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
+                         (bf16*)k_pool, (bf16*)v_pool, block_table, table_stride, store));
     else if (dtype == PE_BF16)
         PE_TRY(pe_launch(rope_store_kernel<bf16>, T, 256, 0, s, (bf16*)qkv, n_q, n_kv, hd, cos_t, sin_t, tok_pos, tok_row,
                                                    (bf16*)k_pool, (bf16*)v_pool, block_table, table_stride, store));
