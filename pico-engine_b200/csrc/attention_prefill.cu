@@ -5,7 +5,7 @@
 //
 // Flash-attention tiling.  Grid: (run of up to 64 consecutive tokens of one sequence, query
 // head); four warps of 16 query rows.  A page of the cache (64 keys of one kv head) is one
-// contiguous tile: the CTA brings key and value pages into shared memory with cp.async, two
+// contiguous tile: the CTA brings key and value pages into shared memory with cp.async, three
 // stages deep, XOR-swizzled in 16-byte chunks so that ldmatrix reads are free of bank
 // conflicts; S = Q.K^T and O += P.V run on mma.sync m16n8k16 with fragments from ldmatrix
 // (values through ldmatrix.trans); softmax statistics are float32 per row in registers.
@@ -23,6 +23,7 @@
 #define AP_WARPS 4                                 // 64 query rows a CTA: several CTAs share an SM and hide each other's waits
 #define AP_QTILE (16 * AP_WARPS)
 #define AP_KTILE PE_PAGE
+#define AP_STAGES 3                                // key/value pages in flight or in use
 #define AP_CHUNKS (AP_HD / 8)                      // 16-byte chunks in a row
 #define AP_SWIZZLE ((AP_CHUNKS % 8) == 0)          // rows of a multiple of 128 bytes: XOR the chunk with the row
 #define AP_NT (AP_HD / 8)                          // 8-wide output tiles
@@ -64,7 +65,7 @@ __device__ __forceinline__ unsigned ap_pack(float lo, float hi) {
 __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
     const bf16* q, int q_stride, bf16* out, const bf16* k_pool, const bf16* v_pool, const int* block_table,
     int table_stride, const int4* tiles, int nh, int nkv, int window, float scale_log2e) {
-    extern __shared__ __align__(128) unsigned char ap_mem[];     // Q [64][HD], then K and V [2 stages][64][HD]
+    extern __shared__ __align__(128) unsigned char ap_mem[];     // Q [64][HD], then K and V [AP_STAGES][64][HD] each
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
 
     const unsigned q_s = ap_smem(ap_mem);
     const unsigned tile_bytes = AP_KTILE * AP_HD * 2;
-    const unsigned k_s = q_s + AP_QTILE * AP_HD * 2, v_s = k_s + 2 * tile_bytes;
+    const unsigned k_s = q_s + AP_QTILE * AP_HD * 2, v_s = k_s + AP_STAGES * tile_bytes;
 
     // the pages the run can see: from the first row's window start to the last row's position
     const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
@@ -100,8 +101,13 @@ __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
         if (row < n) ap_cp16(q_s + ap_offset(row, chunk), q + (size_t)(tok0 + row) * q_stride + (size_t)h * AP_HD + chunk * 8);
         else *reinterpret_cast<uint4*>(ap_mem + ap_offset(row, chunk)) = make_uint4(0u, 0u, 0u, 0u);
     }
-    bool ok_cur = load_page(page_lo, 0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    // the first AP_STAGES - 1 pages are requested at once, one commit group each (empty groups keep the count)
+    bool page_ok[AP_STAGES];
+#pragma unroll
+    for (int i = 0; i < AP_STAGES - 1; ++i) {
+        page_ok[i] = (page_lo + i <= page_hi) && load_page(page_lo + i, i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
 
     // this warp's rows
     const int i_lo = warp * 16 + g, i_hi = i_lo + 8;
@@ -118,12 +124,13 @@ __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
 
     const int mat = lane >> 3, mr = lane & 7;
     for (int pi = page_lo; pi <= page_hi; ++pi) {
-        const int stage = (pi - page_lo) & 1;
-        bool ok_next = false;
-        if (pi < page_hi) ok_next = load_page(pi + 1, stage ^ 1);
+        const int it = pi - page_lo, stage = it % AP_STAGES, ahead = (it + AP_STAGES - 1) % AP_STAGES;
+        asm volatile("cp.async.wait_group %0;" ::"n"(AP_STAGES - 2) : "memory");   // this iteration's page (and Q) have landed
+        __syncthreads();                                          // ... for every thread; and all warps are done with the last page
+        // the page AP_STAGES - 1 ahead goes into the stage that the previous iteration used
+        page_ok[ahead] = (pi + AP_STAGES - 1 <= page_hi) && load_page(pi + AP_STAGES - 1, ahead);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");      // everything but the newest group has landed
-        __syncthreads();
+        const bool ok_cur = page_ok[stage];
         if (pi == page_lo) {
 #pragma unroll
             for (int ks = 0; ks < AP_KS; ++ks)
@@ -195,8 +202,6 @@ __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
                 }
             }
         }
-        __syncthreads();                                          // the stage may be overwritten by the page after next
-        ok_cur = ok_next;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
@@ -226,7 +231,7 @@ extern "C" int pe_attention_prefill(const void* q, int q_stride, void* out, cons
     if (n_tiles <= 0) return 0;
     if (hd != AP_HD || nkv <= 0 || nh % nkv || nh > 65535 || q_stride % 8) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out | (uintptr_t)tiles) & 15) return PE_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(AP_QTILE + 4 * AP_KTILE) * AP_HD * 2;
+    const size_t smem = (size_t)(AP_QTILE + 2 * AP_STAGES * AP_KTILE) * AP_HD * 2;
     static bool attr_set = false;
     if (smem > 48 * 1024 && !attr_set) {
         PE_TRY(cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -117,4 +117,5 @@ def require_cuda(device) -> torch.device:
 
 
 def stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of torch's current CUDA stream (the quick way: no Stream object is made)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
