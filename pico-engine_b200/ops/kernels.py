@@ -243,9 +243,10 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
                      tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
                      max_context: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of T single tokens (bfloat16) over the cache; ``max_context`` bounds every
-    token's position + 1 and fixes the launch shape."""
+    token's position + 1 and fixes the launch shape.  The kernel before this one on the stream may
+    have written keys and values at each token's own position only: older pages are read while
+    that kernel still runs."""
     from .library import for_head_dim
-    from .workspace import scratch
     T = tok_pos.shape[0]
     _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
     if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim):
@@ -256,12 +257,10 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
         out = torch.empty(T, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
     _need(out, "out", torch.bfloat16, (T, n_heads * head_dim))
     lib = for_head_dim(head_dim)
-    nbytes = lib.pe_attention_decode_scratch_bytes(T, n_heads, n_kv_heads, max_context)
-    ws = scratch("attention_decode.partial", nbytes, q.device).data_ptr() if nbytes else None
     check(lib.pe_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
-                                  n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context), ws,
-                                  stream_ptr()), "attention_decode", 2 if nbytes else 1)
+                                  n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context),
+                                  status_word(q.device).data_ptr(), stream_ptr()), "attention_decode")
     return out
 
 

@@ -89,8 +89,6 @@ def for_head_dim(head_dim: int) -> ctypes.CDLL:
         lib = build.load(f"attention_hd{head_dim}", HEAD_DIM_SOURCES, {"PE_HEAD_DIM": str(head_dim)})
         declare(lib, _HEAD_DIM_SIGNATURES)
         lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
-        lib.pe_attention_decode_scratch_bytes.argtypes = [I, I, I, I]
-        lib.pe_attention_decode_scratch_bytes.restype = c_longlong
         _by_head_dim[head_dim] = lib
     return lib
 

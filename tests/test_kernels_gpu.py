@@ -177,6 +177,48 @@ def test_attention_decode(K, nh, nkv, hd, lens, window, max_context):
     assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2), float((got.float().cpu() - want).abs().max())
 
 
+def one_query_attention(q_rows, paged, tok_row, tok_pos, nh, window):
+    """The rows of ``reference_attention`` computed one query at a time (long sequences)."""
+    out = []
+    G = nh // paged.nkv
+    for t, (b, p) in enumerate(zip(tok_row, tok_pos)):
+        lo = 0 if not window else max(0, p - window + 1)
+        k = paged.k[b][lo:p + 1].repeat_interleave(G, dim=1)          # [L, nh, hd]
+        v = paged.v[b][lo:p + 1].repeat_interleave(G, dim=1)
+        s = torch.einsum("hd,lhd->hl", q_rows[t].double(), k.double()) * paged.hd ** -0.5
+        out.append(torch.einsum("hl,lhd->hd", torch.softmax(s, dim=-1), v.double()).float())
+    return torch.stack(out)
+
+
+LONG_CASES = [                        # (nh, nkv, hd, lens, window): what each is there for
+    (4, 2, 64, [3000, 700], None),    # eight page ranges a sequence, merged across the cluster
+    (16, 8, 128, [1100] * 20, None),  # one CTA a sequence and kv head: its ring of pages wraps several times
+    (4, 1, 32, [2500], 1000),         # a window that starts in the middle of a page, many pages back
+    (8, 4, 256, [1500] * 10, None),   # three ranges a sequence, a ring of two pages
+    (7, 1, 64, [4096, 4033, 65], None),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,window", LONG_CASES)
+def test_attention_decode_long(K, nh, nkv, hd, lens, window):
+    paged = Paged(lens, nkv, hd, torch.bfloat16, seed=hd + 3)
+    q, tok_row, tok_pos = attention_case(nh, nkv, hd, lens, window, seed=nh + 9)
+    small = [i for i, p in enumerate(tok_pos) if p < 80]              # the two references agree where both are cheap
+    if small:
+        a = reference_attention(q[small], paged, [tok_row[i] for i in small], [tok_pos[i] for i in small], nh, window)
+        b = one_query_attention(q[small], paged, [tok_row[i] for i in small], [tok_pos[i] for i in small], nh, window)
+        assert torch.allclose(a.reshape(b.shape), b, atol=1e-5)
+    kp, vp, table = paged.cuda()
+    for repeat in range(2):                                            # the second launch finds the barriers' memory used
+        got = K.attention_decode(dev(q.reshape(len(tok_row), -1).to(torch.bfloat16)), nh * hd, nh, nkv, hd, kp, vp, table,
+                                 table.shape[1], dev(torch.tensor(tok_pos, dtype=torch.int32)),
+                                 dev(torch.tensor(tok_row, dtype=torch.int32)), window, hd ** -0.5, max(lens))
+        K.check_status("cuda")
+        want = one_query_attention(q, paged, tok_row, tok_pos, nh, window).reshape(len(tok_row), -1)
+        err = (got.float().cpu() - want).abs().max(dim=1).values
+        assert float(err.max()) < 2e-2, (float(err.max()), tok_row[int(err.argmax())], tok_pos[int(err.argmax())])
+
+
 @pytest.mark.parametrize("nh,nkv,hd,lens,window", CASES)
 @pytest.mark.parametrize("cached", [0, 37])
 def test_attention_prefill(K, nh, nkv, hd, lens, window, cached):
