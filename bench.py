@@ -161,7 +161,10 @@ def main() -> int:
                    "l2": "each step reads 0.99 GB of weights, more than the 126 MB L2",
                    "context_during_timing": f"{CONTEXT - args.steps + 1}..{CONTEXT}", "peaks": pk_kind},
         "e2e": {"value": e2e["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
-                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": e2e["ms_per_step"]},
+                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": e2e["ms_per_step"],
+                "clock": "host clock around Engine.generate's decode steps: token lists in and out, each step's "
+                         "description copied from pinned memory, each step's tokens read back; the loop launches "
+                         "a step before it has read the one in flight, so host work hides behind the device"},
         "gpu_launches": main_run["launches_per_step"] * args.steps,
         "prefill": {"value": pre["tokens_per_s"], "tokens": pre["tokens"], "ms": pre["ms"],
                     "frac": pre["tflops_per_s"] / pk["bf16_tflops"]},

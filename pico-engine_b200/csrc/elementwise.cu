@@ -35,6 +35,23 @@ extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, floa
     return 0;
 }
 
+// Token ids of a step that follows a step still in flight: ids[j] = prev[src[j]] where src[j] >= 0
+// (the token that row src[j] of the step before chose, which the host has not seen yet);
+// other ids stay as the host gave them.
+__global__ void select_tokens_kernel(int* ids, const int* prev, const int* src, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n && src[j] >= 0) ids[j] = prev[src[j]];
+}
+
+extern "C" int pe_select_tokens(int* ids, const int* prev, const int* src, int n, void* stream) {
+    if (n <= 0) return 0;
+    PE_TRY(pe_launch(select_tokens_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, ids, prev, src, n));
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // One block per output row.  `rows_index` (may be null) picks the input row of each output
 // row, so the final norm runs only on the rows whose logits are wanted.

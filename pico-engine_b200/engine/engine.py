@@ -20,7 +20,7 @@ from ..ops.library import core, require_cuda
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_folder, load_into, random_tensor
 from .generate import Request, generate as run_generation, held_tokens
-from .graph import GraphedDecode
+from .graph import GraphedDecode, TokenLoop
 from .step import Stepper
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -67,6 +67,7 @@ class Engine:
         self.cache: Optional[Cache] = None
         self.stepper: Optional[Stepper] = None
         self._graphs = {}
+        self._token_loop: Optional[TokenLoop] = None
         self.last_timing = {}                     # host-clock seconds of the last generate call, by phase
 
     @classmethod
@@ -132,6 +133,7 @@ class EngineBackend:
 
     def __init__(self, engine: Engine, sampler: Sampler, use_graph: bool):
         self.e, self.sampler, self.use_graph = engine, sampler, use_graph
+        self._mark = None                                # when the decode time counted so far ends
 
     def open(self) -> int:
         return self.e.cache.open()
@@ -149,16 +151,21 @@ class EngineBackend:
         self.e.last_timing["prefill_s"] += time.perf_counter() - t0
         return chosen
 
+    def _graph(self, B: int) -> GraphedDecode:
+        key = (B, self.sampler.params)
+        g = self.e._graphs.get(key)
+        if g is None:
+            if self.e._token_loop is None:
+                self.e._token_loop = TokenLoop(self.e.device)
+            g = self.e._graphs[key] = GraphedDecode(self.e.stepper, self.sampler, B, self.e._token_loop)
+        return g
+
     def decode(self, slots, tokens, requests, steps) -> List[int]:
         """One token per sequence in, one chosen token per sequence out, both on the host: the
         step's description is copied from pinned memory, the result is read back."""
         t0, sent = time.perf_counter(), self.e.stepper.h2d_bytes
         if self.use_graph:
-            key = (len(slots), self.sampler.params)
-            g = self.e._graphs.get(key)
-            if g is None:
-                g = self.e._graphs[key] = GraphedDecode(self.e.stepper, self.sampler, len(slots))
-            chosen = g.run(slots, tokens, requests, steps).tolist()
+            chosen = self._graph(len(slots)).launch(slots, tokens, requests, steps).tokens()
         else:
             logits = self.e.stepper.step(slots, [[t] for t in tokens])
             chosen = self.sampler.choose(logits, self._int32(requests), self._int32(steps)).tolist()
@@ -167,3 +174,33 @@ class EngineBackend:
         t["decode_steps"] += 1
         t["h2d_bytes"] += self.e.stepper.h2d_bytes - sent
         return chosen
+
+    # The same step in two halves, so that the loop can launch the next step before it reads this
+    # one's tokens (only with graphs: the next step then takes its ids on the device).
+    @property
+    def pipelined(self) -> bool:
+        return self.use_graph
+
+    def decode_begin(self, slots, tokens, sources, requests, steps):
+        """Launch a decode step.  ``sources[j] >= 0`` names the row of the step launched just before
+        whose chosen token is row j's input (``tokens[j]`` is then ignored)."""
+        now, sent = time.perf_counter(), self.e.stepper.h2d_bytes
+        if self._mark is None:
+            self._mark = now
+        flight = self._graph(len(slots)).launch(slots, [0 if s >= 0 else t for t, s in zip(tokens, sources)],
+                                                requests, steps, sources)
+        t = self.e.last_timing
+        t["decode_steps"] += 1
+        t["h2d_bytes"] += self.e.stepper.h2d_bytes - sent
+        return flight
+
+    def decode_end(self, flight) -> List[int]:
+        chosen = flight.tokens()
+        now = time.perf_counter()
+        self.e.last_timing["decode_s"] += now - self._mark      # wall time since the last step ended (or the first began)
+        self._mark = now
+        return chosen
+
+    def decode_idle(self) -> None:
+        """No step is in flight any more: the time until the next one begins is not decoding."""
+        self._mark = None

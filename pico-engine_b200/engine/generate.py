@@ -32,6 +32,11 @@ class Backend(Protocol):
     def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]], requests: Sequence[int]) -> List[int]: ...
     def decode(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int],
                steps: Sequence[int]) -> List[int]: ...
+    # A backend may also be ``pipelined`` (an attribute that is true) and then has
+    #   decode_begin(slots, tokens, sources, requests, steps) -> handle
+    #   decode_end(handle) -> List[int]
+    # where sources[j] >= 0 names the row of the step begun just before whose chosen token is
+    # row j's input (tokens[j] is then ignored), and optionally decode_idle().
 
 
 class GenerationError(ValueError):
@@ -66,10 +71,34 @@ def plan_batches(requests: Sequence[Request], max_batch: int, max_tokens: int) -
     return batches
 
 
+def _settle(rows: Sequence[Request], chosen: Sequence[int], stop: frozenset) -> None:
+    """Give every row of a step its chosen token: a stop token ends the request (and is neither
+    returned nor fed back), the token that fills ``max_new_tokens`` ends it too.  Rows of
+    requests that had ended before the step was read were computed in vain and are skipped."""
+    if len(chosen) != len(rows):
+        raise GenerationError(f"the backend chose {len(chosen)} tokens for {len(rows)} sequences")
+    for r, tok in zip(rows, chosen):
+        if r.finish_reason:
+            continue
+        if tok in stop:
+            r.finish_reason = "stop"
+        else:
+            r.output.append(int(tok))
+            if len(r.output) >= r.max_new_tokens:
+                r.finish_reason = "length"
+
+
 def run_batch(backend: Backend, batch: Sequence[Request], stop_token_ids: Iterable[int]) -> None:
     """Generate for the requests of one batch, which start together.  A request ends when a
     stop token is chosen (which is neither returned nor fed back) or when it has its
-    ``max_new_tokens``; its slot is given back at once and the others go on."""
+    ``max_new_tokens``; its slot is given back at once and the others go on.
+
+    A backend that is ``pipelined`` (``decode_begin`` / ``decode_end``) is driven one step ahead:
+    the next step is launched before the tokens of the step in flight have been read, for the
+    requests that cannot end by length with those tokens; such a row takes its token from the
+    step in flight.  If a stop token then shows that a request has ended, the row that ran for it
+    is dropped and its slot is given back when that step has been read.  The tokens returned
+    are the same either way."""
     stop = frozenset(stop_token_ids)
     active = [r for r in batch if r.max_new_tokens > 0]
     for r in batch:
@@ -81,22 +110,15 @@ def run_batch(backend: Backend, batch: Sequence[Request], stop_token_ids: Iterab
     try:
         chosen = backend.prefill([slot_of[r.index] for r in active], [r.prompt for r in active],
                                  [r.index for r in active])
+        if getattr(backend, "pipelined", False):
+            _decode_ahead(backend, active, chosen, slot_of, stop)
+            return
         while True:
-            if len(chosen) != len(active):
-                raise GenerationError(f"the backend chose {len(chosen)} tokens for {len(active)} sequences")
-            still: List[Request] = []
-            for r, tok in zip(active, chosen):
-                if tok in stop:
-                    r.finish_reason = "stop"
-                else:
-                    r.output.append(int(tok))
-                    if len(r.output) >= r.max_new_tokens:
-                        r.finish_reason = "length"
+            _settle(active, chosen, stop)
+            for r in active:
                 if r.finish_reason:
                     backend.close(slot_of.pop(r.index))
-                else:
-                    still.append(r)
-            active = still
+            active = [r for r in active if not r.finish_reason]
             if not active:
                 return
             chosen = backend.decode([slot_of[r.index] for r in active], [r.output[-1] for r in active],
@@ -104,6 +126,50 @@ def run_batch(backend: Backend, batch: Sequence[Request], stop_token_ids: Iterab
     finally:
         for slot in slot_of.values():          # only after an error: nothing stays held
             backend.close(slot)
+
+
+def _decode_ahead(backend, rows: List[Request], chosen: Sequence[int], slot_of: dict, stop: frozenset) -> None:
+    """The decode loop of ``run_batch`` for a pipelined backend.  ``chosen`` are the tokens of
+    ``rows``; ``flight`` is the step launched before they were read (None: none)."""
+    flight = None                              # (handle, its rows)
+    unread = []                                # handles of the steps launched and not read, oldest first
+    try:
+        while True:
+            _settle(rows, chosen, stop)
+            flying = {r.index for r in flight[1]} if flight else set()
+            for r in rows:                     # ended, and no launched step still writes its cache
+                if r.finish_reason and r.index in slot_of and r.index not in flying:
+                    backend.close(slot_of.pop(r.index))
+            if flight is None:
+                rows = [r for r in rows if not r.finish_reason]
+                if not rows:
+                    return
+                flight = (backend.decode_begin([slot_of[r.index] for r in rows], [r.output[-1] for r in rows],
+                                               [-1] * len(rows), [r.index for r in rows], [len(r.output) for r in rows]),
+                          rows)
+                unread.append(flight[0])
+            # the step after the one in flight, for those whom its token cannot bring to their length
+            ahead_rows = flight[1]
+            nxt = [r for r in ahead_rows if not r.finish_reason and len(r.output) + 1 < r.max_new_tokens]
+            after = None
+            if nxt:
+                place = {r.index: j for j, r in enumerate(ahead_rows)}
+                after = (backend.decode_begin([slot_of[r.index] for r in nxt], [0] * len(nxt),
+                                              [place[r.index] for r in nxt], [r.index for r in nxt],
+                                              [len(r.output) + 1 for r in nxt]), nxt)
+                unread.append(after[0])
+            handle = unread.pop(0)
+            chosen, rows = backend.decode_end(handle), ahead_rows
+            flight = after
+    finally:
+        for handle in unread:                  # an error: let what was launched end before its slots are given back
+            try:
+                backend.decode_end(handle)
+            except Exception:                  # noqa: BLE001
+                pass
+        idle = getattr(backend, "decode_idle", None)
+        if idle:
+            idle()
 
 
 def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens, stop_token_ids: Iterable[int],

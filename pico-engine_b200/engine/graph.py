@@ -1,6 +1,8 @@
 """One decode step (every row brings one token) captured as a CUDA graph, for a fixed number of
 rows.  All that changes from step to step lives in one int32 device buffer that the host
 refreshes before each replay: token ids, positions, page tables, and the sampling counters.
+A step may also take its token ids from what the step before it chose, on the device, so that
+the host can launch it before it has read those tokens (``TokenLoop``).
 
 pico-engine captures its one-token forward the same way (src/pico_engine/engine.py:269-306):
 static token and position buffers, three warm-up runs on a side stream, replay per token,
@@ -15,64 +17,113 @@ import numpy as np
 import torch
 
 from ..cache import pages_for
+from ..ops import kernels
 from .step import StepLayout, Stepper
 
 
+class InFlight:
+    """A decode step that has been launched: its chosen tokens are on their way to pinned host memory."""
+
+    def __init__(self, B: int, staged: torch.Tensor, done: "torch.cuda.Event"):
+        self.B, self.staged, self.done = B, staged, done
+
+    def tokens(self) -> List[int]:
+        """Wait for the step and return its chosen tokens."""
+        self.done.synchronize()
+        return self.staged[:self.B].tolist()
+
+
+class TokenLoop:
+    """What the decode graphs of one engine share so that a step can follow another without the
+    host in between: the device buffer into which every step writes its chosen tokens (the next
+    step takes its token ids from there) and pinned host buffers for reading them back."""
+
+    ROWS = 4096
+
+    def __init__(self, device):
+        self.chosen = torch.zeros(self.ROWS, dtype=torch.int32, device=device)
+        self._pinned = [torch.zeros(self.ROWS, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._events = [torch.cuda.Event() for _ in range(4)]
+        self._at = 0
+
+    def read_back(self, B: int) -> InFlight:
+        """Copy the tokens the last step chose to the host, in stream order, without waiting."""
+        i = self._at
+        self._at = (i + 1) % len(self._pinned)
+        self._pinned[i][:B].copy_(self.chosen[:B], non_blocking=True)
+        self._events[i].record()
+        return InFlight(B, self._pinned[i], self._events[i])
+
+
 class GraphedDecode:
-    def __init__(self, stepper: Stepper, sampler, B: int):
+    def __init__(self, stepper: Stepper, sampler, B: int, loop: Optional[TokenLoop] = None):
         self.stepper, self.sampler, self.B = stepper, sampler, B
         cache = stepper.cache
+        self.loop = loop or TokenLoop(stepper.device)
+        if B > TokenLoop.ROWS:
+            raise ValueError(f"a decode step of {B} rows is more than the {TokenLoop.ROWS} the token buffer holds")
         self.widths = [pages_for(stepper.max_context)] * len(cache.groups)
         self.layout = StepLayout(B, B, B, self.widths)
         n = self.layout.total
-        self.extra = n                                   # request ids [B], then step counters [B]
-        self.dev = torch.zeros(n + 2 * ((B + 3) & ~3), dtype=torch.int32, device=stepper.device)
+        self.extra = n                                   # request ids [B], step counters [B], token sources [B]
+        self.pad = (B + 3) & ~3
+        self.dev = torch.zeros(n + 3 * self.pad, dtype=torch.int32, device=stepper.device)
         self.host = np.zeros(self.dev.numel(), dtype=np.int32)
-        self.tokens_out = torch.zeros(B, dtype=torch.int32, device=stepper.device)
+        self.tokens_out = self.loop.chosen[:B]
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.failed = False
         self._tables_of: Optional[tuple] = None
 
     # ------------------------------------------------------------------ host side of a step
-    def _fill(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int]) -> None:
-        lay, cache, B = self.layout, self.stepper.cache, self.B
-        lens = [1] * B
-        _, fresh, starts = self.stepper.describe(slots, lens, None, [[t] for t in tokens], self.widths)
+    def _fill(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int],
+              sources: Optional[Sequence[int]]) -> None:
+        lay, B, pad = self.layout, self.B, self.pad
+        _, fresh, starts = self.stepper.describe(slots, [1] * B, None, [[t] for t in tokens], self.widths)
         self.host[:lay.total] = fresh
-        pad = (B + 3) & ~3
         self.host[self.extra: self.extra + B] = np.asarray(requests, dtype=np.int32)
         self.host[self.extra + pad: self.extra + pad + B] = np.asarray(steps, dtype=np.int32)
+        self.host[self.extra + 2 * pad: self.extra + 2 * pad + B] = -1 if sources is None else np.asarray(sources, dtype=np.int32)
         self._starts, self._slots = starts, list(slots)
 
     def _forward(self) -> None:
-        lay, B = self.layout, self.B
-        pad = (B + 3) & ~3
+        lay, B, pad = self.layout, self.B, self.pad
         ctx = self.stepper.context(lay, self.dev, [1] * B, [0] * B, self._slots)
         ctx.max_context = self.stepper.max_context       # launch shapes must not depend on the step
         ctx.starts = [self.stepper.max_context - 1] * B
         ids = self.dev[lay.ids: lay.ids + B]
+        # rows whose token the host has not seen take it from the step before, on the device
+        kernels.select_tokens(ids, self.loop.chosen, self.dev[self.extra + 2 * pad: self.extra + 2 * pad + B])
         self.logits = self.stepper.model.forward(ids, ctx, self.dev[lay.want: lay.want + B])
         self.sampler.choose(self.logits, self.dev[self.extra: self.extra + B],
                             self.dev[self.extra + pad: self.extra + pad + B], self.tokens_out)
 
     def _capture(self) -> None:
+        # The warm-up runs and the capture write the shared token buffer; what the step before chose
+        # is kept aside meanwhile, since this step may take its ids from there.
+        keep = self.loop.chosen.clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(3):                           # the step is idempotent: it rewrites the same cache rows
+                self.loop.chosen.copy_(keep)
                 self._forward()
         torch.cuda.current_stream().wait_stream(side)
+        self.loop.chosen.copy_(keep)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self._forward()
+        self.loop.chosen.copy_(keep)
         self.graph = graph
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
-    def run(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
-        """One decode step of ``B`` rows; returns the chosen tokens (int32 [B], device)."""
-        self._fill(slots, tokens, requests, steps)
+    def launch(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int],
+               sources: Optional[Sequence[int]] = None) -> InFlight:
+        """Start one decode step of ``B`` rows and the copy of its chosen tokens to the host.  Row j's
+        token is ``tokens[j]``, or, where ``sources[j] >= 0``, what row ``sources[j]`` of the step
+        launched before this one chose (``tokens[j]`` is then any valid id)."""
+        self._fill(slots, tokens, requests, steps, sources)
         self.stepper.upload(self.host, self.dev)
         if self.graph is None and not self.failed:
             try:
@@ -86,4 +137,9 @@ class GraphedDecode:
             self._forward()
         for s in slots:
             self.stepper.cache.advance(s, 1)
+        return self.loop.read_back(self.B)
+
+    def run(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
+        """One decode step of ``B`` rows; returns the chosen tokens (int32 [B], device)."""
+        self.launch(slots, tokens, requests, steps)
         return self.tokens_out

@@ -48,6 +48,15 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
+def select_tokens(ids: torch.Tensor, prev: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """``ids[j] = prev[src[j]]`` where ``src[j] >= 0`` (all int32, on the device): the ids of rows whose
+    token the step before chose and the host has not read yet."""
+    n = ids.shape[0]
+    _need(ids, "ids", torch.int32, (n,)); _need(prev, "prev", torch.int32); _need(src, "src", torch.int32, (n,))
+    check(core().pe_select_tokens(ids.data_ptr(), prev.data_ptr(), src.data_ptr(), n, stream_ptr()), "select_tokens")
+    return ids
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
             rows_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """RMSNorm of float32 rows [T, H]; with ``rows_index`` (int32 [R]) only of those rows."""

@@ -17,6 +17,7 @@ HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu")      # compil
 
 _SIGNATURES = {
     "pe_embed": [P, I, P, P, I, I, I, P],
+    "pe_select_tokens": [P, P, P, I, P],
     "pe_rmsnorm": [P, P, P, I, F, P, I, I, I, P],
     "pe_swiglu": [P, P, I, I, I, P],
     "pe_residual_add": [P, P, I, LL, P],

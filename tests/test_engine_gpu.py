@@ -195,6 +195,24 @@ def test_greedy_generation_bfloat16(models, name, use_graph):
     assert exact >= 40
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_decoding_one_step_ahead_changes_no_token(models, name):
+    """With graphs the loop launches a step before it has read the one in flight; without, it does
+    not.  Budgets that differ, stop tokens that fall early, late and on the last token, sampling."""
+    eng, cfg, w = models[(name, "float32")]
+    prompts = list(random_requests(cfg, [3, 30, 8, 21, 2, 14], 23).values())
+    budgets = [1, 20, 7, 20, 2, 13]
+    kw = dict(temperature=0.9, top_k=0, top_p=1.0, seed=11)
+    free = eng.generate(prompts, max_tokens=budgets, use_graph=False, stop_token_ids=(), **kw)
+    stop = (free[1][9], free[3][19], free[5][0])
+    ahead = eng.generate(prompts, max_tokens=budgets, use_graph=True, stop_token_ids=stop, **kw)
+    plainly = eng.generate(prompts, max_tokens=budgets, use_graph=False, stop_token_ids=stop, **kw)
+    assert ahead == plainly
+    assert ahead == [plain.generate(cfg, w, p, m, stop=stop, request=i, **kw) for i, (p, m) in enumerate(zip(prompts, budgets))]
+    assert len(ahead[1]) <= 9 and ahead[5] == [] and len(ahead[0]) <= 1
+    assert not eng.cache.lengths and eng.cache.slots.free_count == eng.cache.max_seqs
+
+
 def test_graph_and_eager_decode_agree(models):
     eng, cfg, w = models[("B", "bfloat16")]
     prompts = list(random_requests(cfg, [20, 70, 3], 20).values())

@@ -88,3 +88,92 @@ def test_slots_are_given_back_after_a_failure():
     with pytest.raises(RuntimeError, match="device lost"):
         generate(be, [[1], [2]], 3, [], 4, 1024)
     assert not be.open_slots
+
+
+# ---------------------------------------------------------------------------- one step ahead
+
+class ScriptedAhead(Scripted):
+    """The same scripted choices through decode_begin / decode_end.  A row may take its token from the
+    step begun just before (``sources``); the backend checks that such a step exists and is still
+    unread, resolves the token itself, and records what ran."""
+
+    pipelined = True
+
+    def __init__(self, script, slots=8):
+        super().__init__(script, slots)
+        self.begun = []            # steps begun and not yet read: (requests, chosen)
+        self.last_begun = None
+        self.most_in_flight = 0
+
+    def decode_begin(self, slots, tokens, sources, requests, steps):
+        resolved = []
+        for tok, src in zip(tokens, sources):
+            if src >= 0:
+                assert self.last_begun is not None, "a source without a step before"
+                resolved.append(self.last_begun[1][src])
+            else:
+                resolved.append(tok)
+        for s in slots:
+            assert s in self.open_slots, "a step on a slot that was given back"
+            self.open_slots[s] += 1
+        chosen = [self.script[r][st] for r, st in zip(requests, steps)]
+        self.calls.append(("decode", list(requests), resolved, list(steps)))
+        handle = (list(requests), chosen, list(slots))
+        self.begun.append(handle)
+        self.last_begun = handle
+        self.most_in_flight = max(self.most_in_flight, len(self.begun))
+        return handle
+
+    def decode_end(self, handle):
+        assert self.begun and self.begun[0] is handle, "steps are read in the order they were begun"
+        self.begun.pop(0)
+        return handle[1]
+
+    def close(self, slot):
+        assert all(slot not in h[2] for h in self.begun), "a slot given back while a step on it is in flight"
+        super().close(slot)
+
+
+def test_one_step_ahead_gives_the_same_tokens_and_feeds_no_stop_token_to_a_live_request():
+    script = {0: [5, 6, 99, 7, 8], 1: [99], 2: [1, 2, 3, 4, 5, 6], 3: [9, 9, 9, 99, 1]}
+    prompts, budget = [[1, 2, 3], [4], [5, 6, 7, 8, 9], [1]], [4, 4, 4, 6]
+    plain = generate(Scripted(script), prompts, budget, stop_token_ids=[99], max_batch=8, max_tokens=4096)
+    be = ScriptedAhead(script)
+    ahead = generate(be, prompts, budget, stop_token_ids=[99], max_batch=8, max_tokens=4096)
+    assert [r.output for r in ahead] == [r.output for r in plain] == [[5, 6], [], [1, 2, 3, 4], [9, 9, 9]]
+    assert [r.finish_reason for r in ahead] == [r.finish_reason for r in plain]
+    assert be.most_in_flight == 2                                           # the loop does run ahead
+    assert not be.open_slots and be.free == list(range(8)) and not be.begun
+    # every step that counts fed each request the token it chose before; rows that ran for a request
+    # that had already stopped are the only extra ones
+    fed = {}
+    for _, requests, tokens, steps in (c for c in be.calls if c[0] == "decode"):
+        for r, t, s in zip(requests, tokens, steps):
+            fed[(r, s)] = t
+    for r in ahead:
+        for s in range(1, len(r.output)):
+            assert fed[(r.index, s)] == r.output[s - 1]
+    extra = [k for k in fed if k[1] > len(ahead[k[0]].output)]
+    assert all(ahead[r].finish_reason == "stop" and s == len(ahead[r].output) + 1 for r, s in extra)
+    # no step is begun for a request that reaches its length with the token in flight
+    assert (2, 4) not in fed and (2, 3) in fed
+
+
+def test_one_step_ahead_batches_and_failures():
+    be = ScriptedAhead({i: [i + 10] * 4 for i in range(5)}, slots=2)
+    reqs = generate(be, [[1]] * 5, 3, stop_token_ids=[], max_batch=2, max_tokens=4096)
+    assert [r.output for r in reqs] == [[i + 10] * 3 for i in range(5)]
+    assert [s for what, s in be.slot_log if what == "open"] == [0, 1, 0, 1, 0]
+    assert not be.begun and not be.open_slots
+
+    class Failing(ScriptedAhead):
+        def decode_end(self, handle):
+            out = super().decode_end(handle)
+            if len([c for c in self.calls if c[0] == "decode"]) >= 2:
+                raise RuntimeError("device lost")
+            return out
+
+    be = Failing({0: [1] * 9, 1: [2] * 9})
+    with pytest.raises(RuntimeError, match="device lost"):
+        generate(be, [[1], [2]], 8, stop_token_ids=[], max_batch=2, max_tokens=4096)
+    assert not be.open_slots and not be.begun                               # nothing stays held or in flight
