@@ -12,7 +12,11 @@
 //
 // At these sizes a product is bound by memory latency, not bandwidth: what counts is how many
 // bytes are in flight and how few dependent trips to memory a kernel makes.  A CTA of eight
-// warps owns 8 or 16 rows of W over all of K (no split over CTAs, hence no second pass).  Its
+// warps owns 8 or 16 rows of W over all of K, or, where K is long and the rows are few (the
+// down projection), over one of `ksplit` ranges of K: the CTAs of the ranges of a tile are a
+// thread-block cluster, and the others send their sums into the first one's shared memory
+// (st.async, counted on an mbarrier there), which adds them in the order of the ranges and
+// runs the epilogue; there is no second pass over global memory.  Its
 // rows are brought into shared memory by bulk asynchronous copies (cp.async.bulk, the 1-D TMA
 // path, completing on an mbarrier), one copy per row and chunk of up to 1024 columns, up to
 // four chunks in flight; registers hold none of it, so many CTAs are resident and the whole
@@ -52,6 +56,7 @@ struct LfArgs {
     int M, N, K;
     int rows;                 // STORE/ACCUM: rows of W per CTA, 8 or 16
     int chunk, stages;        // columns per bulk copy (a multiple of 32) and copies in flight per row
+    int ksplit, kc;           // STORE/ACCUM: ranges of K a tile is cut into (CTAs of a cluster) and columns per range
     int I;                    // SWIGLU
     // ROPE
     int n_q, n_kv, hd;
@@ -83,6 +88,17 @@ __device__ __forceinline__ bool lf_bar_wait(unsigned bar, unsigned parity) {
         __nanosleep(40);
     }
 }
+__device__ __forceinline__ void lf_cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void lf_cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// a float into the shared memory of CTA `rank` of the cluster, at the address it has here; its 4 bytes
+// are counted on that CTA's mbarrier
+__device__ __forceinline__ void lf_send(unsigned local_addr, float v, unsigned local_bar, unsigned rank) {
+    unsigned addr, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(local_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
+}
 __device__ __forceinline__ uint4 lf_lds16(unsigned addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -104,15 +120,24 @@ __device__ __forceinline__ unsigned lf_pack(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// NT: 8-row tiles of sequences (M <= 8 * NT)
-template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_kernel(const LfArgs p, int* status) {
+// CTAs resident per SM that the register budget is set for: the products with many tiles (gate and up,
+// the vocabulary) want as many as their shared memory allows; q/k/v has fewer tiles than the GPU has SMs
+// and takes the registers instead.
+#define LF_MIN_CTAS(NT, EPI) ((EPI) == LF_ROPE ? ((NT) == 1 ? 3 : 2) : ((NT) == 1 ? 5 : 3))
+
+// NT: 8-row tiles of sequences (M <= 8 * NT); SPLIT: a tile's K is cut into ranges over a cluster
+template <int NT, int PRO, int EPI, bool SPLIT>
+__global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fused_kernel(const LfArgs p, int* status) {
     extern __shared__ __align__(128) unsigned char lf_smem[];   // [stage][16 rows][chunk + pad] bfloat16
-    __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES], bars_a[2 * LF_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES], bars_a[2 * LF_MAX_STAGES], bar_x;
     __shared__ float red[LF_WARPS][NT * 4][32];
     __shared__ float ssq[LF_WARPS][NT * 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int K = p.K, M = p.M;
+    const int M = p.M;
+    // the range of K of this CTA (all of it unless the tile is split over a cluster) and its tile
+    const int ksplit = SPLIT ? p.ksplit : 1;
+    const int tile = ksplit > 1 ? blockIdx.x / ksplit : blockIdx.x, ks = ksplit > 1 ? blockIdx.x % ksplit : 0;
+    const int k_begin = ks * p.kc, K = min(p.K, k_begin + p.kc) - k_begin;      // K: columns of this CTA's range
 
     // the rows of W of this tile: group lo feeds MMA rows 0-7, group hi rows 8-15 (hi_base < 0: none)
     int lo_base, hi_base;
@@ -122,13 +147,16 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
         const int half = p.hd >> 1, per_head = half >> 3;
         lo_base = (blockIdx.x / per_head) * p.hd + (blockIdx.x % per_head) * 8; hi_base = lo_base + half;
     } else {
-        lo_base = blockIdx.x * p.rows; hi_base = p.rows == 16 ? lo_base + 8 : -1;
+        lo_base = tile * p.rows; hi_base = p.rows == 16 ? lo_base + 8 : -1;
     }
     const int chunk = p.chunk, n_chunks = (K + chunk - 1) / chunk, stages = p.stages;
     const int tile_rows = hi_base < 0 ? 8 : 16;              // rows of the tile held in shared memory
     const int a_rows = PRO == LF_PLAIN ? NT * 8 : 0;         // PLAIN: the activations of a chunk are staged beside W
     const unsigned row_bytes = (unsigned)(chunk + LF_ROW_PAD) * 2u, stage_bytes = (unsigned)(tile_rows + a_rows) * row_bytes;
     const unsigned smem0 = lf_smem_addr(lf_smem), bar0 = lf_smem_addr(bars), bar_a0 = lf_smem_addr(bars_a);
+    const unsigned bar_x0 = lf_smem_addr(&bar_x);
+    // what the other ranges send: [range - 1][item][low sum, high sum, sum of squares], behind the stages
+    float* gather = reinterpret_cast<float*>(lf_smem + (size_t)stages * stage_bytes);
 
     // row rr (0..15) of the tile in shared memory holds this row of W, or zeros
     const int my_row = lane < 8 ? lo_base + lane : (hi_base < 0 ? -1 : hi_base + lane - 8);
@@ -136,7 +164,9 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { lf_bar_init(bar0 + 8u * s, 1u); lf_bar_init(bar_a0 + 8u * s, 1u); }
+        lf_bar_init(bar_x0, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (ksplit > 1 && ks == 0) lf_bar_expect(bar_x0, (unsigned)((ksplit - 1) * M * 8 * 3 * 4));
     }
     if (warp == 1 && lane < tile_rows && !my_row_ok) {     // rows that no copy fills read as zeros
         for (int s = 0; s < stages; ++s)
@@ -150,6 +180,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                 *reinterpret_cast<uint4*>(lf_smem + s * stage_bytes + (tile_rows + lane) * row_bytes + o) = make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();
+    if (ksplit > 1) lf_cluster_arrive();                     // waited for before the first write to another CTA
 
     // chunk c of every valid row into stage c % stages; called by all of warp 0
     auto issue = [&](int c) {
@@ -160,7 +191,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
         if (lane == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
         __syncwarp();
         if (my_row_ok)
-            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + lane * row_bytes, p.W + (size_t)my_row * K + k0,
+            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + lane * row_bytes, p.W + (size_t)my_row * p.K + k_begin + k0,
                          (unsigned)cols * 2u, bar);
     };
 
@@ -173,13 +204,28 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
         if (lane == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
         __syncwarp();
         if (my_a_ok)
-            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + (tile_rows + lane) * row_bytes, p.A + (size_t)lane * K + k0,
+            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + (tile_rows + lane) * row_bytes, p.A + (size_t)lane * p.K + k_begin + k0,
                          (unsigned)cols * 2u, bar);
     };
 
     pdl_launch_dependents();
     if (warp == 0)                                           // W first: no kernel writes it, so it need not wait
         for (int c = 0; c < n_chunks && c < stages; ++c) issue(c);
+    // ROPE: what the epilogue needs of the step's description (positions, pages) and of the rotation tables is
+    // asked for now: none of it is written by a kernel of the step, and the epilogue then waits for no load.
+    int ep_pos = 0, ep_page = -1;
+    float ep_cos = 1.f, ep_sin = 0.f;
+    if (EPI == LF_ROPE && threadIdx.x < NT * 64) {
+        const int idx = threadIdx.x, j = idx >> 6, e1 = (idx >> 5) & 1, ln = idx & 31;
+        const int r = ln >> 2, m = j * 8 + 2 * (ln & 3) + e1;
+        if (m < M) {
+            const int half = p.hd >> 1, per_head = half >> 3;
+            const int head = blockIdx.x / per_head, d = (blockIdx.x % per_head) * 8 + r;
+            ep_pos = p.tok_pos[m];
+            if (head < p.n_q + p.n_kv && p.cos_t) { ep_cos = p.cos_t[(size_t)ep_pos * half + d]; ep_sin = p.sin_t[(size_t)ep_pos * half + d]; }
+            if (head >= p.n_q && p.store) ep_page = p.block_table[(size_t)p.tok_row[m] * p.table_stride + ep_pos / PE_PAGE];
+        }
+    }
     pdl_wait();                                              // from here on the preceding kernel's results may be read
     if (PRO == LF_PLAIN && warp == 1)
         for (int c = 0; c < n_chunks && c < stages; ++c) issue_a(c);
@@ -200,15 +246,15 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
         const int k0 = c * chunk, cols = min(chunk, K - k0);
 #pragma unroll
         for (int u = 0; u < LF_UNROLL; ++u) {
-            const int col = (warp + u * LF_WARPS) * 32 + t * 8, k = k0 + col;
+            const int col = (warp + u * LF_WARPS) * 32 + t * 8, k = k_begin + k0 + col;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int m = j * 8 + g;
                 a[u][j] = zero;
                 if (c < n_chunks && m < M && col < cols) {
                     if (PRO == LF_RMSNORM) {
-                        const float4 x0 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k);
-                        const float4 x1 = *reinterpret_cast<const float4*>(p.X + (size_t)m * K + k + 4);
+                        const float4 x0 = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + k);
+                        const float4 x1 = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + k + 4);
                         ssq_part[j] += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w +
                                        x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
                         float w8[8];
@@ -227,7 +273,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                         a[u][j].z = lf_pack(x1.x * w8[4], x1.y * w8[5]);
                         a[u][j].w = lf_pack(x1.z * w8[6], x1.w * w8[7]);
                     } else {
-                        a[u][j] = lf_ld16(p.A + (size_t)m * K + k);
+                        a[u][j] = lf_ld16(p.A + (size_t)m * p.K + k);
                     }
                 }
             }
@@ -292,18 +338,32 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     __syncthreads();
 
     // one thread per (sequence, row of the tile's first group); it sums both groups over the warps
+    if (ksplit > 1) lf_cluster_wait();                       // every CTA of the cluster has set up its barrier
     for (int idx = threadIdx.x; idx < NT * 64; idx += 32 * LF_WARPS) {
         const int j = idx >> 6, e1 = (idx >> 5) & 1, ln = idx & 31;
         const int r = ln >> 2, m = j * 8 + 2 * (ln & 3) + e1;
         if (m >= M) continue;
-        float v_lo = 0.f, v_hi = 0.f;
+        float v_lo = 0.f, v_hi = 0.f, sum = 0.f;
 #pragma unroll
         for (int w = 0; w < LF_WARPS; ++w) { v_lo += red[w][j * 4 + e1][ln]; v_hi += red[w][j * 4 + 2 + e1][ln]; }
         if (PRO == LF_RMSNORM) {
-            float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < LF_WARPS; ++w) sum += ssq[w][m];
-            const float rstd = 1.0f / sqrtf(sum / (float)K + p.eps);
+        }
+        if (ksplit > 1) {
+            if (ks != 0) {                                   // this range's sums go to the CTA of the first range
+                const unsigned at = lf_smem_addr(gather + ((size_t)(ks - 1) * NT * 64 + idx) * 3);
+                lf_send(at, v_lo, bar_x0, 0u); lf_send(at + 4u, v_hi, bar_x0, 0u); lf_send(at + 8u, sum, bar_x0, 0u);
+                continue;
+            }
+            if (!lf_bar_wait(bar_x0, 0u)) { atomicExch(status, 2); continue; }
+            for (int o = 0; o < ksplit - 1; ++o) {           // in the order of the ranges
+                const float* g3 = gather + ((size_t)o * NT * 64 + idx) * 3;
+                v_lo += g3[0]; v_hi += g3[1]; sum += g3[2];
+            }
+        }
+        if (PRO == LF_RMSNORM) {
+            const float rstd = 1.0f / sqrtf(sum / (float)p.K + p.eps);
             v_lo *= rstd; v_hi *= rstd;
         }
 
@@ -322,10 +382,9 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
             if (p.bias) { v_lo += load_as_f(p.bias, p.bias_dtype, n_lo); v_hi += load_as_f(p.bias, p.bias_dtype, n_hi); }
             // the unfused path rounds the projection to bfloat16 before it rotates; so does this one
             v_lo = __bfloat162float(__float2bfloat16_rn(v_lo)); v_hi = __bfloat162float(__float2bfloat16_rn(v_hi));
-            const int pos = p.tok_pos[m];
+            const int pos = ep_pos;                          // loaded before the main loop (this thread's own m and d)
             if (head < p.n_q + p.n_kv && p.cos_t) {
-                const float c = p.cos_t[(size_t)pos * half + d], s = p.sin_t[(size_t)pos * half + d];
-                const float a = v_lo * c - v_hi * s, b = v_lo * s + v_hi * c;
+                const float a = v_lo * ep_cos - v_hi * ep_sin, b = v_lo * ep_sin + v_hi * ep_cos;
                 v_lo = a; v_hi = b;
             }
             const bf16 o_lo = __float2bfloat16_rn(v_lo), o_hi = __float2bfloat16_rn(v_hi);
@@ -333,7 +392,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                 bf16* q = (bf16*)p.out + (size_t)m * p.n_q * p.hd + (size_t)head * p.hd;
                 q[d] = o_lo; q[d + half] = o_hi;
             } else if (p.store) {
-                const int page = p.block_table[(size_t)p.tok_row[m] * p.table_stride + pos / PE_PAGE];
+                const int page = ep_page;
                 if (page >= 0) {
                     const bool is_k = head < p.n_q + p.n_kv;
                     const int kvh = head - p.n_q - (is_k ? 0 : p.n_kv);
@@ -343,7 +402,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
                 }
             }
         } else {
-            const int n_lo = blockIdx.x * p.rows + r, n_hi = n_lo + 8;
+            const int n_lo = tile * p.rows + r, n_hi = n_lo + 8;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int n = h ? n_hi : n_lo;
@@ -359,22 +418,38 @@ __global__ void __launch_bounds__(32 * LF_WARPS, NT == 1 ? 5 : 3) linear_fused_k
     }
 }
 
-template <int NT, int PRO, int EPI>
+template <int NT, int PRO, int EPI, bool SPLIT>
 static int lf_launch_nt(const LfArgs& a, int tiles, size_t smem, int* status, cudaStream_t s) {
     static size_t allowed = 36 * 1024;                       // per instantiation: dynamic shared memory opted into (the
     if (smem > allowed) {                                    // kernel's static arrays take up to 9 KB of the default 48 KB)
-        PE_TRY(cudaFuncSetAttribute(linear_fused_kernel<NT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PE_TRY(cudaFuncSetAttribute(linear_fused_kernel<NT, PRO, EPI, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         allowed = smem;
     }
-    PE_TRY(pe_launch(linear_fused_kernel<NT, PRO, EPI>, tiles, 32 * LF_WARPS, smem, s, a, status));
+    if (SPLIT) PE_TRY(pe_launch_cluster(linear_fused_kernel<NT, PRO, EPI, SPLIT>, tiles * a.ksplit, 32 * LF_WARPS, smem, s, (unsigned)a.ksplit, a, status));
+    else PE_TRY(pe_launch(linear_fused_kernel<NT, PRO, EPI, SPLIT>, tiles, 32 * LF_WARPS, smem, s, a, status));
     return 0;
 }
+
+// The most ranges of K a tile is cut into (a tuning knob: 1 = never, up to 8).
+static int& lf_ksplit_limit() { static int limit = 8; return limit; }
+extern "C" void pe_linear_fused_set_max_ksplit(int n) { lf_ksplit_limit() = n < 1 ? 1 : (n > 8 ? 8 : n); }
 
 template <int PRO, int EPI>
 static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
     if (!status) return PE_ERR_UNSUPPORTED;
-    a.chunk = a.K >= LF_MAX_CHUNK ? LF_MAX_CHUNK : (a.K + 31) / 32 * 32;
-    const int n_chunks = (a.K + a.chunk - 1) / a.chunk;
+    // A long K with few tiles (fewer CTAs than the GPU has SMs): cut K into ranges, one CTA each, up to
+    // 8 to a cluster, while the grid stays within two to three CTAs an SM.
+    a.ksplit = 1;
+    if (EPI != LF_SWIGLU && EPI != LF_ROPE && a.K > LF_MAX_CHUNK) {
+        int want = (a.K + LF_MAX_CHUNK - 1) / LF_MAX_CHUNK;
+        if (want > lf_ksplit_limit()) want = lf_ksplit_limit();
+        while (want > 1 && (long long)tiles * want * 2 > 5 * 148) --want;     // measured: about 2.3 CTAs an SM is best
+        a.ksplit = want;
+    }
+    a.kc = a.ksplit > 1 ? ((a.K + a.ksplit - 1) / a.ksplit + 31) / 32 * 32 : a.K;
+    // chunks of equal length (a short last chunk costs a whole turn of the pipeline)
+    const int n_chunks = (a.kc + LF_MAX_CHUNK - 1) / LF_MAX_CHUNK;
+    a.chunk = ((a.kc + n_chunks - 1) / n_chunks + 31) / 32 * 32;
     const int nt = a.M <= 8 ? 1 : 2;
     const int tile_rows = (EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? 16 : 8;
     const size_t stage = (size_t)(tile_rows + (PRO == LF_PLAIN ? nt * 8 : 0)) * (a.chunk + LF_ROW_PAD) * 2;
@@ -382,9 +457,14 @@ static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
     if (max_stages > 2 * LF_MAX_STAGES) max_stages = 2 * LF_MAX_STAGES;
     if (max_stages < 1) max_stages = 1;
     a.stages = n_chunks < max_stages ? n_chunks : max_stages;
-    const size_t smem = (size_t)a.stages * stage;
-    if (nt == 1) return lf_launch_nt<1, PRO, EPI>(a, tiles, smem, status, s);
-    return lf_launch_nt<2, PRO, EPI>(a, tiles, smem, status, s);
+    const size_t smem = (size_t)a.stages * stage + (size_t)(a.ksplit - 1) * nt * 64 * 3 * 4;
+    constexpr bool can_split = EPI != LF_SWIGLU && EPI != LF_ROPE;
+    if (can_split && a.ksplit > 1) {
+        if (nt == 1) return lf_launch_nt<1, PRO, EPI, can_split>(a, tiles, smem, status, s);
+        return lf_launch_nt<2, PRO, EPI, can_split>(a, tiles, smem, status, s);
+    }
+    if (nt == 1) return lf_launch_nt<1, PRO, EPI, false>(a, tiles, smem, status, s);
+    return lf_launch_nt<2, PRO, EPI, false>(a, tiles, smem, status, s);
 }
 
 static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }

@@ -411,7 +411,8 @@ def test_sample_draws_do_not_depend_on_the_batch(K):
 # ---------------------------------------------------------------------------- fused decode products
 
 @pytest.mark.parametrize("M", [1, 8, 13, 16])
-@pytest.mark.parametrize("N,K_", [(100, 96), (896, 896), (896, 4864), (9728, 896), (70, 160), (5000, 3584)])
+@pytest.mark.parametrize("N,K_", [(100, 96), (896, 896), (896, 4864), (9728, 896), (70, 160), (5000, 3584),
+                                  (40, 9000), (100, 2080)])      # the last two: K cut into 8 and 3 ranges over a cluster
 def test_linear_fused(K, M, N, K_):
     a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
     want = a.double() @ w.double().T
