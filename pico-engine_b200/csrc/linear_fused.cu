@@ -123,14 +123,16 @@ __device__ __forceinline__ unsigned lf_pack(float lo, float hi) {
 // CTAs resident per SM that the register budget is set for: the products with many tiles (gate and up,
 // the vocabulary) want as many as their shared memory allows; q/k/v has fewer tiles than the GPU has SMs
 // and takes the registers instead.
-#define LF_MIN_CTAS(NT, EPI) ((EPI) == LF_ROPE ? ((NT) == 1 ? 3 : 2) : ((NT) == 1 ? 5 : 3))
+#define LF_MIN_CTAS(NT, RT, EPI) (((EPI) == LF_ROPE || (RT) == 2) ? ((NT) == 1 ? 3 : 2) : ((NT) == 1 ? 5 : 3))
 
-// NT: 8-row tiles of sequences (M <= 8 * NT); SPLIT: a tile's K is cut into ranges over a cluster
-template <int NT, int PRO, int EPI, bool SPLIT>
-__global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fused_kernel(const LfArgs p, int* status) {
-    extern __shared__ __align__(128) unsigned char lf_smem[];   // [stage][16 rows][chunk + pad] bfloat16
+// NT: 8-row tiles of sequences (M <= 8 * NT); RT: 16-row tiles of W a CTA takes (2 where a product has
+// so many tiles that the activations, which every CTA reads, would cost as much as the weights);
+// SPLIT: a tile's K is cut into ranges over a cluster
+template <int NT, int RT, int PRO, int EPI, bool SPLIT>
+__global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linear_fused_kernel(const LfArgs p, int* status) {
+    extern __shared__ __align__(128) unsigned char lf_smem[];   // [stage][16 * RT rows][chunk + pad] bfloat16
     __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES], bars_a[2 * LF_MAX_STAGES], bar_x;
-    __shared__ float red[LF_WARPS][NT * 4][32];
+    __shared__ float red[LF_WARPS][RT * NT * 4][32];
     __shared__ float ssq[LF_WARPS][NT * 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int M = p.M;
@@ -139,18 +141,20 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
     const int tile = ksplit > 1 ? blockIdx.x / ksplit : blockIdx.x, ks = ksplit > 1 ? blockIdx.x % ksplit : 0;
     const int k_begin = ks * p.kc, K = min(p.K, k_begin + p.kc) - k_begin;      // K: columns of this CTA's range
 
-    // the rows of W of this tile: group lo feeds MMA rows 0-7, group hi rows 8-15 (hi_base < 0: none)
+    // the rows of W of this tile: group lo feeds MMA rows 0-7, group hi rows 8-15 (hi_base < 0: none);
+    // with RT = 2 the second 16-row tile follows at lo_base + rt_step, hi_base + rt_step
     int lo_base, hi_base;
+    const int rt_step = EPI == LF_SWIGLU ? 8 : 16;
     if (EPI == LF_SWIGLU) {
-        lo_base = blockIdx.x * 8; hi_base = p.I + lo_base;
+        lo_base = blockIdx.x * 8 * RT; hi_base = p.I + lo_base;
     } else if (EPI == LF_ROPE) {
         const int half = p.hd >> 1, per_head = half >> 3;
         lo_base = (blockIdx.x / per_head) * p.hd + (blockIdx.x % per_head) * 8; hi_base = lo_base + half;
     } else {
-        lo_base = tile * p.rows; hi_base = p.rows == 16 ? lo_base + 8 : -1;
+        lo_base = tile * p.rows * RT; hi_base = p.rows == 16 ? lo_base + 8 : -1;
     }
     const int chunk = p.chunk, n_chunks = (K + chunk - 1) / chunk, stages = p.stages;
-    const int tile_rows = hi_base < 0 ? 8 : 16;              // rows of the tile held in shared memory
+    const int tile_rows = hi_base < 0 ? 8 : 16 * RT;         // rows of the tile held in shared memory
     const int a_rows = PRO == LF_PLAIN ? NT * 8 : 0;         // PLAIN: the activations of a chunk are staged beside W
     const unsigned row_bytes = (unsigned)(chunk + LF_ROW_PAD) * 2u, stage_bytes = (unsigned)(tile_rows + a_rows) * row_bytes;
     const unsigned smem0 = lf_smem_addr(lf_smem), bar0 = lf_smem_addr(bars), bar_a0 = lf_smem_addr(bars_a);
@@ -158,9 +162,11 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
     // what the other ranges send: [range - 1][item][low sum, high sum, sum of squares], behind the stages
     float* gather = reinterpret_cast<float*>(lf_smem + (size_t)stages * stage_bytes);
 
-    // row rr (0..15) of the tile in shared memory holds this row of W, or zeros
-    const int my_row = lane < 8 ? lo_base + lane : (hi_base < 0 ? -1 : hi_base + lane - 8);
-    const bool my_row_ok = lane < tile_rows && my_row >= 0 && my_row < p.N;
+    // row rr of the tile in shared memory (16 a tile: 8 of group lo, 8 of group hi) holds this row of W, or zeros
+    const int my_rt = lane >> 4, my_l = lane & 15;
+    const int my_row = my_l < 8 ? lo_base + my_rt * rt_step + my_l : (hi_base < 0 ? -1 : hi_base + my_rt * rt_step + my_l - 8);
+    const bool my_row_ok = lane < tile_rows && my_row >= 0 && my_row < p.N &&
+                           (EPI != LF_SWIGLU || my_l >= 8 || my_row < p.I);   // a gate row past I is no gate row
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { lf_bar_init(bar0 + 8u * s, 1u); lf_bar_init(bar_a0 + 8u * s, 1u); }
@@ -237,9 +243,11 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
 #pragma unroll
     for (int j = 0; j < NT; ++j) ssq_part[j] = 0.f;
 
-    float acc[NT][4];
+    float acc[RT][NT][4];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[rt][j][0] = acc[rt][j][1] = acc[rt][j][2] = acc[rt][j][3] = 0.f;
 
     // the activations of this warp's steps of chunk c (a chunk has at most LF_WARPS * LF_UNROLL steps)
     auto load_a = [&](int c, uint4 (&a)[LF_UNROLL][NT]) {
@@ -297,14 +305,21 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
             const int step = warp + u * LF_WARPS, col = step * 32 + t * 8;
             if (step < steps) {                              // the same for all lanes of the warp: the MMA needs them all
                 const bool in = col < cols;                  // a last step may be narrower than 32 columns
-                const uint4 wa = in ? lf_lds16(stage + g * row_bytes + col * 2) : zero;
-                const uint4 wb = (in && tile_rows == 16) ? lf_lds16(stage + (8 + g) * row_bytes + col * 2) : zero;
+                uint4 wa[RT], wb[RT];
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    wa[rt] = in ? lf_lds16(stage + (rt * 16 + g) * row_bytes + col * 2) : zero;
+                    wb[rt] = (in && tile_rows >= 16) ? lf_lds16(stage + (rt * 16 + 8 + g) * row_bytes + col * 2) : zero;
+                }
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
                     const uint4 a = PRO == LF_PLAIN ? (in ? lf_lds16(stage + (tile_rows + j * 8 + g) * row_bytes + col * 2) : zero)
                                                     : a_cur[u][j];
-                    lf_mma(acc[j], wa.x, wb.x, wa.y, wb.y, a.x, a.y);
-                    lf_mma(acc[j], wa.z, wb.z, wa.w, wb.w, a.z, a.w);
+#pragma unroll
+                    for (int rt = 0; rt < RT; ++rt) {
+                        lf_mma(acc[rt][j], wa[rt].x, wb[rt].x, wa[rt].y, wb[rt].y, a.x, a.y);
+                        lf_mma(acc[rt][j], wa[rt].z, wb[rt].z, wa[rt].w, wb[rt].w, a.z, a.w);
+                    }
                 }
             }
         }
@@ -321,11 +336,13 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
         }
     }
 
-    // acc[j][e] of lane (g, t): MMA row g (+8 if e & 2), sequence j*8 + 2t + (e & 1)
+    // acc[rt][j][e] of lane (g, t): MMA row g (+8 if e & 2) of tile rt, sequence j*8 + 2t + (e & 1)
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
+    for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) red[warp][j * 4 + e][lane] = acc[j][e];
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red[warp][(rt * NT + j) * 4 + e][lane] = acc[rt][j][e];
     if (PRO == LF_RMSNORM) {
 #pragma unroll
         for (int j = 0; j < NT; ++j) {                       // lanes (g, 0..3) hold parts of row j*8 + g
@@ -339,13 +356,13 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
 
     // one thread per (sequence, row of the tile's first group); it sums both groups over the warps
     if (ksplit > 1) lf_cluster_wait();                       // every CTA of the cluster has set up its barrier
-    for (int idx = threadIdx.x; idx < NT * 64; idx += 32 * LF_WARPS) {
-        const int j = idx >> 6, e1 = (idx >> 5) & 1, ln = idx & 31;
+    for (int idx = threadIdx.x; idx < RT * NT * 64; idx += 32 * LF_WARPS) {
+        const int rt = idx / (NT * 64), j = (idx >> 6) % NT, e1 = (idx >> 5) & 1, ln = idx & 31;
         const int r = ln >> 2, m = j * 8 + 2 * (ln & 3) + e1;
         if (m >= M) continue;
         float v_lo = 0.f, v_hi = 0.f, sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < LF_WARPS; ++w) { v_lo += red[w][j * 4 + e1][ln]; v_hi += red[w][j * 4 + 2 + e1][ln]; }
+        for (int w = 0; w < LF_WARPS; ++w) { v_lo += red[w][(rt * NT + j) * 4 + e1][ln]; v_hi += red[w][(rt * NT + j) * 4 + 2 + e1][ln]; }
         if (PRO == LF_RMSNORM) {
 #pragma unroll
             for (int w = 0; w < LF_WARPS; ++w) sum += ssq[w][m];
@@ -368,7 +385,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
         }
 
         if (EPI == LF_SWIGLU) {
-            const int i = blockIdx.x * 8 + r;
+            const int i = blockIdx.x * 8 * RT + rt * 8 + r;
             if (i < p.I) {
                 // the unfused path rounds gate and up to bfloat16 before the activation; so does this one
                 v_lo = __bfloat162float(__float2bfloat16_rn(v_lo)); v_hi = __bfloat162float(__float2bfloat16_rn(v_hi));
@@ -402,7 +419,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
                 }
             }
         } else {
-            const int n_lo = tile * p.rows + r, n_hi = n_lo + 8;
+            const int n_lo = tile * p.rows * RT + rt * 16 + r, n_hi = n_lo + 8;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int n = h ? n_hi : n_lo;
@@ -418,17 +435,26 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, EPI)) linear_fu
     }
 }
 
-template <int NT, int PRO, int EPI, bool SPLIT>
+template <int NT, int RT, int PRO, int EPI, bool SPLIT>
 static int lf_launch_nt(const LfArgs& a, int tiles, size_t smem, int* status, cudaStream_t s) {
-    static size_t allowed = 36 * 1024;                       // per instantiation: dynamic shared memory opted into (the
-    if (smem > allowed) {                                    // kernel's static arrays take up to 9 KB of the default 48 KB)
-        PE_TRY(cudaFuncSetAttribute(linear_fused_kernel<NT, PRO, EPI, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t allowed = 0;                               // per instantiation: dynamic shared memory that may be asked for
+    if (allowed == 0) {                                      // (without opting in: 48 KB less the kernel's static arrays)
+        cudaFuncAttributes fa;
+        PE_TRY(cudaFuncGetAttributes(&fa, linear_fused_kernel<NT, RT, PRO, EPI, SPLIT>));
+        allowed = 48 * 1024 - fa.sharedSizeBytes;
+    }
+    if (smem > allowed) {
+        PE_TRY(cudaFuncSetAttribute(linear_fused_kernel<NT, RT, PRO, EPI, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         allowed = smem;
     }
-    if (SPLIT) PE_TRY(pe_launch_cluster(linear_fused_kernel<NT, PRO, EPI, SPLIT>, tiles * a.ksplit, 32 * LF_WARPS, smem, s, (unsigned)a.ksplit, a, status));
-    else PE_TRY(pe_launch(linear_fused_kernel<NT, PRO, EPI, SPLIT>, tiles, 32 * LF_WARPS, smem, s, a, status));
+    if (SPLIT) PE_TRY(pe_launch_cluster(linear_fused_kernel<NT, RT, PRO, EPI, SPLIT>, tiles * a.ksplit, 32 * LF_WARPS, smem, s, (unsigned)a.ksplit, a, status));
+    else PE_TRY(pe_launch(linear_fused_kernel<NT, RT, PRO, EPI, SPLIT>, (tiles + RT - 1) / RT, 32 * LF_WARPS, smem, s, a, status));
     return 0;
 }
+
+// Whether products with many tiles take two 16-row tiles a CTA (a tuning knob).
+static int& lf_two_tiles() { static int on = 1; return on; }
+extern "C" void pe_linear_fused_set_two_tiles(int on) { lf_two_tiles() = on ? 1 : 0; }
 
 // The most ranges of K a tile is cut into (a tuning knob: 1 = never, up to 8).
 static int& lf_ksplit_limit() { static int limit = 8; return limit; }
@@ -451,7 +477,11 @@ static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
     const int n_chunks = (a.kc + LF_MAX_CHUNK - 1) / LF_MAX_CHUNK;
     a.chunk = ((a.kc + n_chunks - 1) / n_chunks + 31) / 32 * 32;
     const int nt = a.M <= 8 ? 1 : 2;
-    const int tile_rows = (EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? 16 : 8;
+    // Two 16-row tiles a CTA where a product has so many tiles that the activations, which every CTA reads
+    // again, would cost as much as the weights (gate and up, the vocabulary), and enough CTAs remain.
+    constexpr bool can_two = EPI == LF_SWIGLU || EPI == LF_STORE_F32;
+    const bool two = can_two && a.ksplit == 1 && (EPI == LF_SWIGLU || a.rows == 16) && tiles >= 2 * 148 && lf_two_tiles();
+    const int tile_rows = two ? 32 : ((EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? 16 : 8);
     const size_t stage = (size_t)(tile_rows + (PRO == LF_PLAIN ? nt * 8 : 0)) * (a.chunk + LF_ROW_PAD) * 2;
     int max_stages = (int)((160u << 10) / stage);            // chunks in flight: what fits in 160 KB, at most 8
     if (max_stages > 2 * LF_MAX_STAGES) max_stages = 2 * LF_MAX_STAGES;
@@ -460,11 +490,15 @@ static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
     const size_t smem = (size_t)a.stages * stage + (size_t)(a.ksplit - 1) * nt * 64 * 3 * 4;
     constexpr bool can_split = EPI != LF_SWIGLU && EPI != LF_ROPE;
     if (can_split && a.ksplit > 1) {
-        if (nt == 1) return lf_launch_nt<1, PRO, EPI, can_split>(a, tiles, smem, status, s);
-        return lf_launch_nt<2, PRO, EPI, can_split>(a, tiles, smem, status, s);
+        if (nt == 1) return lf_launch_nt<1, 1, PRO, EPI, can_split>(a, tiles, smem, status, s);
+        return lf_launch_nt<2, 1, PRO, EPI, can_split>(a, tiles, smem, status, s);
     }
-    if (nt == 1) return lf_launch_nt<1, PRO, EPI, false>(a, tiles, smem, status, s);
-    return lf_launch_nt<2, PRO, EPI, false>(a, tiles, smem, status, s);
+    if (can_two && two) {
+        if (nt == 1) return lf_launch_nt<1, can_two ? 2 : 1, PRO, EPI, false>(a, tiles, smem, status, s);
+        return lf_launch_nt<2, can_two ? 2 : 1, PRO, EPI, false>(a, tiles, smem, status, s);
+    }
+    if (nt == 1) return lf_launch_nt<1, 1, PRO, EPI, false>(a, tiles, smem, status, s);
+    return lf_launch_nt<2, 1, PRO, EPI, false>(a, tiles, smem, status, s);
 }
 
 static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }

@@ -412,7 +412,8 @@ def test_sample_draws_do_not_depend_on_the_batch(K):
 
 @pytest.mark.parametrize("M", [1, 8, 13, 16])
 @pytest.mark.parametrize("N,K_", [(100, 96), (896, 896), (896, 4864), (9728, 896), (70, 160), (5000, 3584),
-                                  (40, 9000), (100, 2080)])      # the last two: K cut into 8 and 3 ranges over a cluster
+                                  (40, 9000), (100, 2080),       # K cut into 8 and 3 ranges over a cluster
+                                  (4744, 512)])                  # two row tiles a CTA, the last CTA has one
 def test_linear_fused(K, M, N, K_):
     a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
     want = a.double() @ w.double().T
@@ -441,7 +442,8 @@ def test_linear_fused_rows_do_not_depend_on_their_neighbours(K):
         assert torch.equal(K.linear_fused(dev(a[rows].to(torch.bfloat16)), W, out_dtype=torch.float32), whole[rows])
 
 
-@pytest.mark.parametrize("M,H,I", [(1, 64, 160), (8, 896, 4864), (16, 96, 352), (5, 3584, 1000)])
+@pytest.mark.parametrize("M,H,I", [(1, 64, 160), (8, 896, 4864), (16, 96, 352), (5, 3584, 1000), (13, 512, 2504),
+                                   (16, 896, 4864)])           # the last three take two row tiles a CTA; 2504 / 8 is odd
 def test_norm_gate_up_swiglu(K, M, H, I):
     x, nw = rnd(M, H, seed=1, scale=2.0), bf(1 + rnd(H, seed=2) * 0.1)
     w = bf(rnd(2 * I, H, seed=3, scale=H ** -0.5))
