@@ -199,8 +199,13 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
     if out is None:
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, (B,))
-    check(core().pe_sample(logits.data_ptr(), out.data_ptr(), B, V, float(temperature), int(top_k), float(top_p),
-                           int(seed) & ((1 << 64) - 1), request.data_ptr(), step.data_ptr(), stream_ptr()), "sample")
+    from .workspace import scratch
+    lib = core()
+    ws = scratch("sample.state", lib.pe_sample_scratch_bytes(B, V), logits.device, zeroed=True)
+    cut_k, cut_p = 0 < top_k < V, top_p < 1.0
+    check(lib.pe_sample(logits.data_ptr(), out.data_ptr(), B, V, float(temperature), int(top_k), float(top_p),
+                        int(seed) & ((1 << 64) - 1), request.data_ptr(), step.data_ptr(), ws.data_ptr(), stream_ptr()),
+          "sample", 2 + 3 * cut_k + 3 * cut_p)
     return out
 
 

@@ -26,7 +26,7 @@ _SIGNATURES = {
     "pe_linear_simt": [P, I, P, I, P, I, P, I, I, I, I, P],
     "pe_attention_generic": [P, I, P, P, P, I, P, I, P, P, I, I, I, I, I, F, P],
     "pe_argmax": [P, P, I, I, P, P],
-    "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P],
+    "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P, P],
     "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
     "pe_linear_mma_splits": [I, I],
     "pe_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, P, P],
@@ -70,6 +70,8 @@ def core() -> ctypes.CDLL:
         lib.pe_draw_uniform.restype = c_float
         lib.pe_argmax_scratch_bytes.argtypes = [I, I]
         lib.pe_argmax_scratch_bytes.restype = c_longlong
+        lib.pe_sample_scratch_bytes.argtypes = [I, I]
+        lib.pe_sample_scratch_bytes.restype = c_longlong
         lib.pe_linear_mma_scratch_bytes.argtypes = [I, I, I]
         lib.pe_linear_mma_scratch_bytes.restype = c_longlong
         _core = lib

@@ -377,7 +377,7 @@ def test_argmax(K, V):
     assert got == logits.argmax(dim=-1).tolist() and got[2] == 17 and got[3] == V - 1
 
 
-@pytest.mark.parametrize("V", [257, 5000])
+@pytest.mark.parametrize("V", [257, 5000, 151936])             # 1, 2 and 38 chunks a row
 @pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.8, 0, 1.0), (0.7, 0, 0.9), (1.3, 5, 1.0),
                                                      (1.0, 40, 0.5), (0.5, 1, 1.0), (2.0, 0, 0.05)])
 def test_sample_equals_the_plain_sampler(K, V, temperature, top_k, top_p):
@@ -389,6 +389,8 @@ def test_sample_equals_the_plain_sampler(K, V, temperature, top_k, top_p):
     want = [plain.sample(logits[b], temperature, top_k, top_p, plain.uniform_for(1234, int(request[b]), int(step[b])))
             for b in range(B)]
     assert got == want
+    again = K.sample(dev(logits), temperature, top_k, top_p, 1234, dev(request), dev(step)).cpu().tolist()
+    assert again == got                                            # the kernels leave their state clean
     assert all(abs(K.draw_uniform(1234, r, s) - plain.uniform_for(1234, r, s)) == 0 for r in (0, 5) for s in (0, 9))
 
 
