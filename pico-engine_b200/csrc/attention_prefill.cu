@@ -154,18 +154,28 @@ __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
                     ap_mma(s[2 * jj + 1], qf[ks], b[2], b[3]);
                 }
             // scale, mask, running maximum.  s[j][e]: row (e & 2 ? g + 8 : g), key key0 + j*8 + 2t + (e & 1)
+            // A page that every row of the warp sees whole (before the diagonal, inside the window) needs no mask.
+            const bool whole = key0 + AP_KTILE - 1 <= w_first && w_last < pos0 + n && warp * 16 + 16 <= n &&
+                               (window <= 0 || w_last - key0 < window);
             float tmax[2] = {-INFINITY, -INFINITY};
+            if (whole) {
 #pragma unroll
-            for (int j = 0; j < AP_KTILE / 8; ++j)
+                for (int j = 0; j < AP_KTILE / 8; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + j * 8 + 2 * t + (e & 1);
-                    const int p = (e & 2) ? p_hi : p_lo;
-                    const bool see = ((e & 2) ? row_hi : row_lo) && key <= p && (window <= 0 || p - key < window);
-                    const float v = see ? s[j][e] * scale_log2e : -INFINITY;
-                    s[j][e] = v;
-                    tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
-                }
+                    for (int e = 0; e < 4; ++e) tmax[e >> 1] = fmaxf(tmax[e >> 1], s[j][e]);
+                tmax[0] *= scale_log2e; tmax[1] *= scale_log2e;
+            } else {
+#pragma unroll
+                for (int j = 0; j < AP_KTILE / 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + 2 * t + (e & 1);
+                        const int p = (e & 2) ? p_hi : p_lo;
+                        const bool see = ((e & 2) ? row_hi : row_lo) && key <= p && (window <= 0 || p - key < window);
+                        if (!see) s[j][e] = -INFINITY;
+                        tmax[e >> 1] = fmaxf(tmax[e >> 1], s[j][e] * scale_log2e);
+                    }
+            }
             float alpha[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -176,17 +186,21 @@ __global__ void __launch_bounds__(32 * AP_WARPS) attention_prefill_kernel(
                 m_run[r] = m_new;
                 l_run[r] *= alpha[r];
             }
+            // a row that has seen no key yet has the maximum -inf: its exponents are taken against 0, and are all 0
+            const float m_use[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};
 #pragma unroll
             for (int j = 0; j < AP_KTILE / 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = (s[j][e] == -INFINITY) ? 0.f : ap_exp2(s[j][e] - m_run[e >> 1]);
+                    const float pv = ap_exp2(fmaf(s[j][e], scale_log2e, -m_use[e >> 1]));      // 2^-inf = 0
                     s[j][e] = pv;
                     l_run[e >> 1] += pv;
                 }
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {                 // seldom after the first pages
 #pragma unroll
-            for (int j = 0; j < AP_NT; ++j) {
-                o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+                for (int j = 0; j < AP_NT; ++j) {
+                    o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+                }
             }
 #pragma unroll
             for (int kk = 0; kk < AP_KTILE / 16; ++kk) {         // 16 keys at a time
