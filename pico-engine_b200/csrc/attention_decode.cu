@@ -64,13 +64,17 @@ __device__ __forceinline__ void ad_bulk_copy(unsigned dst, const void* src, unsi
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // true when the phase with this parity has completed; false when the wait ran out
+__device__ __forceinline__ bool ad_bar_test(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0u;
+}
 __device__ __forceinline__ bool ad_bar_wait(unsigned bar, unsigned parity) {
+    if (ad_bar_test(bar, parity)) return true;               // the usual case costs one test
     const long long deadline = clock64() + AD_WAIT_CYCLES;
     for (;;) {
-        unsigned done;
-        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
+        if (ad_bar_test(bar, parity)) return true;
         if (clock64() > deadline) return false;
         __nanosleep(32);
     }
@@ -315,6 +319,7 @@ __global__ void __launch_bounds__(AD_THREADS, 1) attention_decode_kernel(
             qf[c][1] = (cin && r_hi < G) ? ad_ld16(qp + (size_t)(kvh * G + r_hi) * AD_HD) : zero;
         }
         const int grp = warp >> 2, first_key = (warp & 3) * 16;
+        const bool wraps = n_mine > stages;
         bool dead = false;
         int s = grp % stages, round = grp / stages;
         for (int i = grp; i < n_mine; i += AD_GROUPS) {
@@ -339,8 +344,10 @@ __global__ void __launch_bounds__(AD_THREADS, 1) attention_decode_kernel(
                 }
                 ad_consume(acc, m_run, l_run, qf, kt, vt, key0, lo, pos, scale_log2e, g, t);
             }
-            __syncwarp();
-            if (lane == 0) ad_bar_arrive(empty0 + 8u * s);
+            if (wraps) {                                     // a stage that is used again: tell the producer it is free
+                __syncwarp();
+                if (lane == 0) ad_bar_arrive(empty0 + 8u * s);
+            }
             s += AD_GROUPS;
             while (s >= stages) { s -= stages; ++round; }
         }
@@ -486,7 +493,7 @@ static int ad_clusters_at_once(int splits, size_t smem) {
 }
 
 // The most page ranges a sequence is cut into (a tuning knob: 1 .. AD_MAX_SPLITS).
-static int& ad_split_limit() { static int limit = 8; return limit; }
+static int& ad_split_limit() { static int limit = AD_MAX_SPLITS; return limit; }
 extern "C" void pe_attention_decode_set_max_splits(int n) { ad_split_limit() = n < 1 ? 1 : (n > AD_MAX_SPLITS ? AD_MAX_SPLITS : n); }
 
 // The launch shape for T tokens over at most `max_context` keys each: how many page ranges a
