@@ -198,16 +198,26 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                                     *reinterpret_cast<uint4*>(o + i) = make_uint4(w[0], w[1], w[2], w[3]);
                                 }
                             }
-                        } else {                                    // ACCUM into the float32 residual stream
-                            float* o = (float*)p.out + (size_t)row * p.N + n0 + c;
+                        }
+                    }
+                    if (EPI == GT_ACCUM) {
+                        // Into the float32 residual stream (the sum stays float32, as in the decode kernels).  A lane
+                        // holds a row, so the warp turns its 32 x 32 block through shared memory (the stages are free:
+                        // every MMA has read them) and then adds row by row, 32 lanes to 128 contiguous bytes.
+                        float* turn = reinterpret_cast<float*>(gt_mem + (stage0 - gt_smem(gt_mem))) + quarter * (32 * 33);
+                        __syncwarp();
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                if (n0 + c + i < p.N) {             // N is a multiple of 8
-                                    float4 x = *reinterpret_cast<float4*>(o + i);   // the sum stays float32, as in the decode kernels
-                                    x.x += acc[i]; x.y += acc[i + 1]; x.z += acc[i + 2]; x.w += acc[i + 3];
-                                    *reinterpret_cast<float4*>(o + i) = x;
-                                }
-                            }
+                        for (int i = 0; i < 32; ++i) turn[lane * 33 + i] = acc[i];
+                        __syncwarp();
+                        const int col = n0 + c + lane;
+                        if (col < p.N) {
+                            float* o = (float*)p.out + (size_t)(m0 + quarter * 32) * p.N + col;
+                            const int rows = min(32, p.M - (m0 + quarter * 32));
+                            float x[32];                             // all loads first: they do not wait for one another
+#pragma unroll
+                            for (int r = 0; r < 32; ++r) x[r] = r < rows ? o[(size_t)r * p.N] : 0.f;
+#pragma unroll
+                            for (int r = 0; r < 32; ++r) if (r < rows) o[(size_t)r * p.N] = x[r] + turn[r * 33 + lane];
                         }
                     }
                 }
