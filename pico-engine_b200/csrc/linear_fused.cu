@@ -452,6 +452,12 @@ static int lf_launch_nt(const LfArgs& a, int tiles, size_t smem, int* status, cu
     return 0;
 }
 
+// For a K of several chunks: kilobytes of a stage and of all stages of a CTA (tuning knobs; 0: one CTA an SM
+// with chunks of up to 1024 columns).
+static int& lf_stage_kb() { static int kb = 48; return kb; }      // measured at the 7B shape: 2 stages of 48 KB, 2 CTAs an SM
+static int& lf_budget_kb() { static int kb = 108; return kb; }     // (3.4 TB/s against 2.4 TB/s with one CTA an SM and 58 KB stages)
+extern "C" void pe_linear_fused_set_stage_policy(int stage_kb, int budget_kb) { lf_stage_kb() = stage_kb; lf_budget_kb() = budget_kb; }
+
 // Whether products with many tiles take two 16-row tiles a CTA (a tuning knob).
 static int& lf_two_tiles() { static int on = 1; return on; }
 extern "C" void pe_linear_fused_set_two_tiles(int on) { lf_two_tiles() = on ? 1 : 0; }
@@ -473,17 +479,28 @@ static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
         a.ksplit = want;
     }
     a.kc = a.ksplit > 1 ? ((a.K + a.ksplit - 1) / a.ksplit + 31) / 32 * 32 : a.K;
-    // chunks of equal length (a short last chunk costs a whole turn of the pipeline)
-    const int n_chunks = (a.kc + LF_MAX_CHUNK - 1) / LF_MAX_CHUNK;
-    a.chunk = ((a.kc + n_chunks - 1) / n_chunks + 31) / 32 * 32;
     const int nt = a.M <= 8 ? 1 : 2;
     // Two 16-row tiles a CTA where a product has so many tiles that the activations, which every CTA reads
     // again, would cost as much as the weights (gate and up, the vocabulary), and enough CTAs remain.
     constexpr bool can_two = EPI == LF_SWIGLU || EPI == LF_STORE_F32;
     const bool two = can_two && a.ksplit == 1 && (EPI == LF_SWIGLU || a.rows == 16) && tiles >= 2 * 148 && lf_two_tiles();
     const int tile_rows = two ? 32 : ((EPI == LF_SWIGLU || EPI == LF_ROPE || a.rows == 16) ? 16 : 8);
-    const size_t stage = (size_t)(tile_rows + (PRO == LF_PLAIN ? nt * 8 : 0)) * (a.chunk + LF_ROW_PAD) * 2;
-    int max_stages = (int)((160u << 10) / stage);            // chunks in flight: what fits in 160 KB, at most 8
+    const int rows_total = tile_rows + (PRO == LF_PLAIN ? nt * 8 : 0);
+    // Chunks of equal length (a short last chunk costs a whole turn of the pipeline).  A range of K that fits
+    // one chunk is one chunk.  A longer one is cut so that a stage is about lf_stage_kb() and a CTA holds about
+    // lf_budget_kb(): several CTAs then share an SM and stream while another starts up or runs its epilogue.
+    int cap = LF_MAX_CHUNK;
+    size_t budget = 160u << 10;
+    if (a.kc > LF_MAX_CHUNK && lf_stage_kb() > 0) {
+        cap = ((lf_stage_kb() << 10) / (rows_total * 2) - LF_ROW_PAD) / 32 * 32;
+        if (cap < 128) cap = 128;
+        if (cap > LF_MAX_CHUNK) cap = LF_MAX_CHUNK;
+        budget = (size_t)lf_budget_kb() << 10;
+    }
+    const int n_chunks = (a.kc + cap - 1) / cap;
+    a.chunk = ((a.kc + n_chunks - 1) / n_chunks + 31) / 32 * 32;
+    const size_t stage = (size_t)rows_total * (a.chunk + LF_ROW_PAD) * 2;
+    int max_stages = (int)(budget / stage);                  // chunks in flight: what fits the budget, at most 8
     if (max_stages > 2 * LF_MAX_STAGES) max_stages = 2 * LF_MAX_STAGES;
     if (max_stages < 1) max_stages = 1;
     a.stages = n_chunks < max_stages ? n_chunks : max_stages;
