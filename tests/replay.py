@@ -137,7 +137,7 @@ def plain_logits(cfg: dict, weights: dict, requests: dict) -> dict:
     import plain_qwen2 as plain
     out = {}
     for rid, toks in requests.items():
-        logits = plain.forward(cfg, weights, toks).numpy()
+        logits = plain.forward(cfg, weights, toks).cpu().numpy()
         for p in range(len(toks)):
             out[(rid, p)] = logits[p]
     return out

@@ -1,0 +1,46 @@
+"""The engine at the layer sizes of real Qwen2.5 models (fewer layers, random weights) against the
+plain implementation, which here runs on the GPU in float32 (its matrix products are the
+library's float32 ones: no reduced-precision mode is enabled).  Every way of cutting: whole
+prompts, the last tokens one by one, a batch of unequal lengths whose shorter requests end earlier."""
+import gc
+
+import pytest
+import torch
+
+import replay
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [("qwen2.5-0.5b", 2, 3), ("qwen2.5-7b", 1, 4), ("qwen2.5-14b", 1, 5)]      # (shape, layers kept, seed)
+LENGTHS = [70, 33, 5, 129]
+
+
+def _setup(name, layers, seed):
+    from pico_engine.config import config_from_dict
+    from pico_engine.config.registry import architecture
+    from pico_engine.config.shapes import shape
+    from pico_engine.weights import random_tensor
+    d = shape(name)
+    d["num_hidden_layers"] = layers
+    cfg = config_from_dict(d)
+    expected = architecture(cfg.ARCHITECTURE).build_model(cfg, torch.bfloat16, "meta").expected_tensors()
+    weights = {n: random_tensor(n, spec, seed, torch.bfloat16, "cuda").float() for n, spec in expected.items()}
+    g = torch.Generator().manual_seed(seed)
+    reqs = {f"r{i}": torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for i, n in enumerate(LENGTHS)}
+    want = replay.plain_logits(d, weights, reqs)
+    del weights
+    gc.collect(); torch.cuda.empty_cache()
+    return cfg, reqs, want
+
+
+@pytest.mark.parametrize("name,layers,seed", SHAPES, ids=[s[0] for s in SHAPES])
+def test_real_layer_sizes_every_way_of_cutting(name, layers, seed):
+    from pico_engine.engine.engine import Engine
+    cfg, reqs, want = _setup(name, layers, seed)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_config(cfg, seed=seed, draw_on="cuda", dtype=dtype)
+        replay.compare(replay.run_in_process(eng, replay.whole(reqs)), want, dtype, f"{name} whole")
+        replay.compare(replay.run_in_process(eng, replay.tail(reqs, 8)), want, dtype, f"{name} tail")
+        replay.compare(replay.run_in_process(eng, replay.batched(reqs, 3, 0.4)), want, dtype, f"{name} batched")
+        del eng
+        gc.collect(); torch.cuda.empty_cache()
