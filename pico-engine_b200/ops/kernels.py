@@ -355,18 +355,18 @@ def check_status(device) -> None:
         raise KernelError(f"a kernel gave up a bounded wait (status {code}); its results are incomplete")
 
 
-# A weight this large whose rows are longer than one chunk of the fused kernel (1024 columns) streams faster
-# through the library's product even for a few rows: measured on a B200 at 8 rows, 37888 x 3584 (271 MB):
-# 46 us (5.9 TB/s) against 61 us; 3584 x 18944 (136 MB): 28 us against 33 us.  Smaller weights, and long
-# weights with short rows (a vocabulary of 151936 x 896), are faster in the fused kernels.
-FUSED_MAX_LONG_WEIGHT_BYTES = int(os.environ.get("PICO_ENGINE_FUSED_MAX_MB", "100")) << 20
+# A weight this large streams faster through the library's product even for a few rows: measured on a B200 at
+# 8 rows, 37888 x 3584 (271 MB): 46 us (5.9 TB/s) against 61 us; 3584 x 18944 (136 MB): 28 us against 33 us;
+# 151936 x 896 (272 MB, into float32): 52 us against 72 us.  The fused kernel's CTAs restart their pipeline
+# for every tile; smaller weights are faster there, with what precedes and follows the product fused in.
+FUSED_MAX_WEIGHT_BYTES = int(os.environ.get("PICO_ENGINE_FUSED_MAX_MB", "100")) << 20
 
 
 def fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor) -> bool:
     """Whether the fused decode kernels take a product with ``rows`` rows and weight ``w``."""
     return (rows <= FUSED_MAX_ROWS and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.is_contiguous()
             and w.data_ptr() % 16 == 0 and all(t.is_contiguous() and t.data_ptr() % 16 == 0 for t in others)
-            and (w.shape[1] <= 1024 or w.numel() * 2 <= FUSED_MAX_LONG_WEIGHT_BYTES))
+            and w.numel() * 2 <= FUSED_MAX_WEIGHT_BYTES)
 
 
 def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor] = None,
