@@ -91,7 +91,9 @@ def run(model, cfg: dict, seed: int, tokens, prefills, decode_from: int) -> dict
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py PATH_TO_PICO_ENGINE_CHECKOUT")
+    root = sys.argv[1]
     model = load_reference(root)
     g = torch.Generator().manual_seed(1234)
     result = {}
