@@ -10,7 +10,7 @@
 // bytes in flight do not depend on registers or on how many warps are resident.  The copies
 // start before this kernel waits for the one before it: that kernel can have written only the
 // newest token's key and value, and the warp that meets this row fetches it again after the
-// wait.  The consumer warps (16 for head sizes up to 64, else 8) take 16 keys of a page each:
+// wait.  The consumer warps (8 or 16, see below) take 16 keys of a page each:
 // scores S = Q.K^T with mma.sync m16n8k16 (16-byte loads from shared memory straight into B
 // fragments, the head dimension permuted identically in Q), online softmax in float32 on the
 // accumulator registers, then O += P.V where V fragments are transposed in registers with
@@ -36,17 +36,18 @@
 
 #define AD_HD PE_HEAD_DIM
 #define AD_NCHUNK ((AD_HD + 31) / 32)
-#define AD_WARPS (AD_HD <= 64 ? 16 : 8)              // consumer warps (what the registers allow); warp AD_WARPS is the producer
-#define AD_GROUPS (AD_WARPS / 4)                     // pages under way at once: four warps share a page
-#define AD_THREADS (32 * (AD_WARPS + 1))
+// The kernel is compiled for 8 and for 16 consumer warps (one more warp is the producer).  Four warps share a
+// page, so 2 or 4 pages are under way at once.  16 warps (one CTA an SM) are quicker where few sequences
+// have long contexts; 8 warps (two CTAs an SM for head sizes up to 64) everywhere else.
+#define AD_CTAS(WARPS) (((WARPS) == 16 || AD_HD > 64) ? 1 : 2)
 #define AD_MAX_STAGES 12                             // pages in flight per CTA
 #define AD_MAX_SPLITS 16                             // page ranges of a sequence = CTAs of a cluster (8 is the portable limit)
 #define AD_KV_BYTES (PE_PAGE * AD_HD * 2)            // the keys (or the values) of one page and kv head
 #define AD_STAGE_BYTES (2 * AD_KV_BYTES)
 #define AD_ROW (AD_HD + 2)                           // floats between the rows of a warp's partial sums (skews the banks)
 #define AD_RES_BYTES ((16 * (AD_HD + 3 * AD_MAX_SPLITS) * 4 + 127) / 128 * 128)   // what the merge of the ranges gathers
-#define AD_SCRATCH_BYTES (AD_WARPS * 16 * (AD_ROW + 2) * 4)
-#define AD_SMEM_BUDGET (190 * 1024)                  // leaves room on the SM for the next kernel's first CTAs
+#define AD_SCRATCH_BYTES(WARPS) ((WARPS) * 16 * (AD_ROW + 2) * 4)
+#define AD_SMEM_BUDGET(WARPS) ((AD_CTAS(WARPS) == 2 ? 108 : 190) * 1024)   // per CTA; leaves room for the next kernel's first CTAs
 #define AD_WAIT_CYCLES 2000000000ll                  // about a second of SM clock
 
 __device__ __forceinline__ unsigned ad_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -210,11 +211,13 @@ __device__ __forceinline__ void ad_consume(float (&acc)[AD_NCHUNK][4][4], float 
     }
 }
 
-__global__ void __launch_bounds__(AD_THREADS, 1) attention_decode_kernel(
+template <int AD_WARPS>
+__global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attention_decode_kernel(
     const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool,
     const int* block_table, int table_stride, const int* tok_pos,
     const int* tok_row, int nh, int nkv, int window, float scale_log2e, int n_splits, int stages,
     int* status, bf16* out) {
+    constexpr int AD_GROUPS = AD_WARPS / 4, AD_THREADS = 32 * (AD_WARPS + 1);
     extern __shared__ __align__(128) unsigned char ad_smem[];   // result rows, then the ring (later: the warps' partial results)
     __shared__ __align__(8) unsigned long long bars[2 * AD_MAX_STAGES + 1];
     __shared__ int page_ok[AD_MAX_STAGES];                      // whether the stage holds a page (written by the producer)
@@ -446,80 +449,141 @@ __global__ void __launch_bounds__(AD_THREADS, 1) attention_decode_kernel(
 extern "C" int pe_attention_decode_head_dim() { return AD_HD; }
 extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }
 
-static size_t ad_smem_bytes(int stages) {
-    size_t body = (size_t)stages * AD_STAGE_BYTES;
-    if (body < AD_SCRATCH_BYTES) body = AD_SCRATCH_BYTES;
-    return AD_RES_BYTES + body;
-}
+// The host side of one variant of the kernel.  In an unnamed namespace: the libraries of several head sizes
+// live in one process, and the function-local statics of a template with external linkage would be one
+// object for all of them (the dynamic linker makes such symbols unique across libraries).
+namespace {
+template <int WARPS>
+struct AdVariant {
+    static constexpr int threads = 32 * (WARPS + 1), groups = WARPS / 4, ctas_per_sm = AD_CTAS(WARPS);
 
-static int ad_allow_smem(size_t smem) {
-    static size_t allowed = 48 * 1024 - 512;
-    static bool wide = false;
-    if (!wide) {                                             // clusters of more than 8 CTAs are an opt-in; if it is refused,
-        cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // the occupancy
-        cudaGetLastError();                                  // query below answers 0 for them and fewer ranges are used
-        wide = true;
+    static size_t smem_bytes(int stages) {
+        size_t body = (size_t)stages * AD_STAGE_BYTES;
+        if (body < (size_t)AD_SCRATCH_BYTES(WARPS)) body = AD_SCRATCH_BYTES(WARPS);
+        return AD_RES_BYTES + body;
     }
-    if (smem > allowed) {
-        PE_TRY(cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        allowed = smem;
-    }
-    return 0;
-}
 
-// How many clusters of `splits` CTAs with this much shared memory the GPU holds at once (a
-// cluster needs its SMs in one GPC, so this is less than SMs x CTAs per SM / splits); 0 on error.
-static int ad_clusters_at_once(int splits, size_t smem) {
-    static std::mutex lock;
-    static std::map<std::pair<int, size_t>, int> known;
-    std::lock_guard<std::mutex> hold(lock);
-    auto it = known.find({splits, smem});
-    if (it != known.end()) return it->second;
-    int n = 0;
-    if (ad_allow_smem(smem) == 0) {
+    static int allow_smem(size_t smem) {
+        static size_t allowed = 48 * 1024 - 512;
+        static bool wide = false;
+        if (!wide) {                                         // clusters of more than 8 CTAs are an opt-in; if it is refused,
+            cudaFuncSetAttribute(attention_decode_kernel<WARPS>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // the
+            cudaGetLastError();                              // occupancy query below answers 0 for them and fewer ranges are used
+            wide = true;
+        }
+        if (smem > allowed) {
+            PE_TRY(cudaFuncSetAttribute(attention_decode_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            allowed = smem;
+        }
+        return 0;
+    }
+
+    // How many clusters of `splits` CTAs with this much shared memory the GPU holds at once (a
+    // cluster needs its SMs in one GPC, so this is less than SMs x CTAs per SM / splits); 0 on error.
+    static int clusters_at_once(int splits, size_t smem) {
+        static std::mutex lock;
+        static std::map<std::pair<int, size_t>, int> known;
+        std::lock_guard<std::mutex> hold(lock);
+        auto it = known.find({splits, smem});
+        if (it != known.end()) return it->second;
+        int n = 0;
+        if (allow_smem(smem) == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(splits, 1, 148 * ctas_per_sm);
+            cfg.blockDim = dim3(threads);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<WARPS>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        }
+        known[{splits, smem}] = n;
+        return n;
+    }
+
+    // The launch shape for `ctas` (token, kv head, head tile) triples over at most `pages` pages each: how many
+    // page ranges a sequence is cut into and how many pages a CTA keeps in flight.  As many ranges as fill the
+    // GPU once, and no more than let all clusters be resident at the same time.
+    static int shape(int ctas, int pages, int limit, int* stages_out) {
+        const int fit = (AD_SMEM_BUDGET(WARPS) - AD_RES_BYTES) / AD_STAGE_BYTES;
+        int splits = 148 * ctas_per_sm / ctas;
+        if (splits > limit) splits = limit;
+        if (splits > pages) splits = pages;
+        if (splits < 1) splits = 1;
+        int stages = 1;
+        for (;; --splits) {
+            const int most = (pages + splits - 1) / splits;  // pages of a CTA's range
+            stages = most;
+            if (stages > fit) stages = fit;
+            if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;
+            // A ring that is used more than once has a multiple of `groups` stages: a stage then always serves
+            // the same warps, which therefore see every phase of its barriers (see the kernel).
+            if (stages < most) stages -= stages % groups;
+            if (splits == 1 || stages < 1 || clusters_at_once(splits, smem_bytes(stages)) >= ctas) break;
+        }
+        *stages_out = stages;
+        return splits;
+    }
+
+    static int launch(dim3 grid, int n_splits, int stages, cudaStream_t stream, const bf16* q, int q_stride, const bf16* k_pool,
+                      const bf16* v_pool, const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
+                      int nh, int nkv, int window, float scale_log2e, int* status, bf16* out) {
+        const size_t smem = smem_bytes(stages);
+        { const int e = allow_smem(smem); if (e) return e; }
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(splits, 1, 148 * 1);
-        cfg.blockDim = dim3(AD_THREADS);
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(threads);
         cfg.dynamicSmemBytes = smem;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int n_attr = 0;
+        if (pe_pdl_enabled()) {
+            attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+            ++n_attr;
+        }
+        if (n_splits > 1) {
+            attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+            attr[n_attr].val.clusterDim.x = n_splits; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
+            ++n_attr;
+        }
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        cfg.numAttrs = n_attr;
+        PE_TRY(cudaLaunchKernelEx(&cfg, attention_decode_kernel<WARPS>, q, q_stride, k_pool, v_pool, block_table, table_stride,
+                                  tok_pos, tok_row, nh, nkv, window, scale_log2e, n_splits, stages, status, out));
+        PE_LAUNCH_CHECK();
+        return 0;
     }
-    known[{splits, smem}] = n;
-    return n;
-}
+};
+}  // namespace
 
 // The most page ranges a sequence is cut into (a tuning knob: 1 .. AD_MAX_SPLITS).
 static int& ad_split_limit() { static int limit = AD_MAX_SPLITS; return limit; }
 extern "C" void pe_attention_decode_set_max_splits(int n) { ad_split_limit() = n < 1 ? 1 : (n > AD_MAX_SPLITS ? AD_MAX_SPLITS : n); }
 
-// The launch shape for T tokens over at most `max_context` keys each: how many page ranges a
-// sequence is cut into and how many pages a CTA keeps in flight.  A function of these sizes
-// (and of the GPU) only, never of the sequences' lengths: the same launch is replayed as
-// sequences grow.  As many ranges as fill the GPU once, and no more than let all clusters be
-// resident at the same time.
-extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_context, int* stages_out) {
+// Which variant and shape a launch takes: a function of the launch's sizes (and of the GPU) only, never of
+// the sequences' lengths: the same launch is replayed as sequences grow.  Measured at head size 64: 16 warps
+// win where at most 32 CTA-triples have 8 or more pages each (8 sequences of 4,096 tokens: 8.1 us against
+// 8.3 us), 8 warps elsewhere (1 sequence: 4.9 us against 5.3 us; 64 sequences: 24 us against 27 us).
+static bool ad_choose(int T, int nh, int nkv, int max_context, int* splits_out, int* stages_out) {
     const int G = nh / nkv, ctas = T * nkv * ((G + 15) / 16);
     const int pages = (max_context + PE_PAGE - 1) / PE_PAGE;
-    const int fit = (AD_SMEM_BUDGET - AD_RES_BYTES) / AD_STAGE_BYTES;
-    int splits = 148 * 1 / ctas;
-    if (splits > ad_split_limit()) splits = ad_split_limit();
-    if (splits > pages) splits = pages;
-    if (splits < 1) splits = 1;
-    int stages = 1;
-    for (;; --splits) {
-        const int most = (pages + splits - 1) / splits;      // pages of a CTA's range
-        stages = most;
-        if (stages > fit) stages = fit;
-        if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;
-        // A ring that is used more than once has a multiple of AD_GROUPS stages: a stage then always serves
-        // the same warps, which therefore see every phase of its barriers (see the kernel).
-        if (stages < most) stages -= stages % AD_GROUPS;
-        if (splits == 1 || stages < 1 || ad_clusters_at_once(splits, ad_smem_bytes(stages)) >= ctas) break;
+    if constexpr (AD_HD <= 64) {                             // larger heads need the registers: 8 warps only
+        if (ctas <= 32) {
+            int stages = 0;
+            const int splits = AdVariant<16>::shape(ctas, pages, ad_split_limit(), &stages);
+            if ((pages + splits - 1) / splits >= 8) { *splits_out = splits; *stages_out = stages; return true; }
+        }
     }
+    *splits_out = AdVariant<8>::shape(ctas, pages, ad_split_limit(), stages_out);
+    return false;
+}
+
+extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_context, int* stages_out) {
+    int splits = 1, stages = 1;
+    ad_choose(T, nh, nkv, max_context, &splits, &stages);
     if (stages_out) *stages_out = stages;
     return splits;
 }
@@ -531,35 +595,20 @@ extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const
     if (T <= 0) return 0;
     if (hd != AD_HD || nkv <= 0 || nh % nkv || max_context <= 0 || q_stride % 8 || T > 65535 || !status) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) return PE_ERR_UNSUPPORTED;
-    int stages = 0;
-    const int n_splits = pe_attention_decode_splits(T, nh, nkv, max_context, &stages);
-    if (stages < 1) return PE_ERR_UNSUPPORTED;
     const int G = nh / nkv;
     if ((long long)nkv * ((G + 15) / 16) > 65535) return PE_ERR_UNSUPPORTED;
-    const size_t smem = ad_smem_bytes(stages);
-    { const int e = ad_allow_smem(smem); if (e) return e; }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_splits, nkv * ((G + 15) / 16), T);
-    cfg.blockDim = dim3(AD_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[2];
-    int n_attr = 0;
-    if (pe_pdl_enabled()) {
-        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
-        ++n_attr;
+    int n_splits = 1, stages = 0;
+    const bool wide = ad_choose(T, nh, nkv, max_context, &n_splits, &stages);
+    if (stages < 1) return PE_ERR_UNSUPPORTED;
+    const dim3 grid(n_splits, nkv * ((G + 15) / 16), T);
+    const float scale_log2e = scale * 1.4426950408889634f;
+    if constexpr (AD_HD <= 64) {
+        if (wide)
+            return AdVariant<16>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
+                                         (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window,
+                                         scale_log2e, status, (bf16*)out);
     }
-    if (n_splits > 1) {
-        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-        attr[n_attr].val.clusterDim.x = n_splits; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
-        ++n_attr;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = n_attr;
-    PE_TRY(cudaLaunchKernelEx(&cfg, attention_decode_kernel, (const bf16*)q, q_stride, (const bf16*)k_pool,
-                              (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window,
-                              scale * 1.4426950408889634f, n_splits, stages, status, (bf16*)out));
-    PE_LAUNCH_CHECK();
-    return 0;
+    return AdVariant<8>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
+                                (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window, scale_log2e,
+                                status, (bf16*)out);
 }
