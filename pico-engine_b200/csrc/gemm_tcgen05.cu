@@ -95,7 +95,6 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     // shared memory for the stages, 1024-byte aligned as the swizzle needs
     const unsigned stage0 = (gt_smem(gt_mem) + 1023u) & ~1023u;
 
-    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < GT_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gt_smem(&full_bar[s])) : "memory");
@@ -112,6 +111,9 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = tmem_base_s;
+    // Only now may the next kernel of the stream be scheduled: if it came earlier, took tensor memory on this SM
+    // and then waited for this grid to end, a CTA of this grid that still had to allocate would wait for it in turn.
+    pdl_launch_dependents();
     pdl_wait();
 
     if (warp == 0) {

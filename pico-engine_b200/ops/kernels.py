@@ -279,29 +279,26 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
     return out
 
 
-PREFILL_TILE = 64     # AP_QTILE of csrc/attention_prefill.cu
+PREFILL_TILE = 64             # AP_QTILE of csrc/attention_prefill.cu
+PREFILL_TILE_TCGEN05 = 128    # AT_QTILE of csrc/attention_prefill_tcgen05.cu
+TCGEN05_HEAD_DIMS = (64, 128)
 
 
-def prefill_tiles(lens, starts, device) -> torch.Tensor:
+def prefill_tiles(lens, starts, device, tile: int = PREFILL_TILE) -> torch.Tensor:
     """int32 [tiles, 4] = (batch row, first packed token, tokens, position of the first token):
-    the packed tokens of a step cut into runs of at most 64 tokens of one sequence, the runs that
-    see the most keys first (they take longest, so they are scheduled first)."""
+    the packed tokens of a step cut into runs of at most ``tile`` tokens of one sequence, the runs
+    that see the most keys first (they take longest, so they are scheduled first)."""
     rows = []
     tok = 0
     for b, (n, st) in enumerate(zip(lens, starts)):
-        for off in range(0, n, PREFILL_TILE):
-            rows.append((b, tok + off, min(PREFILL_TILE, n - off), st + off))
+        for off in range(0, n, tile):
+            rows.append((b, tok + off, min(tile, n - off), st + off))
         tok += n
     rows.sort(key=lambda r: -(r[3] + r[2]))
     return torch.tensor(rows, dtype=torch.int32).to(device, non_blocking=True)
 
 
-def attention_prefill(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
-                      tiles: torch.Tensor, n_tokens: int, window: Optional[int], scale: float,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal attention (bfloat16) of the token runs ``tiles`` over the cache."""
-    from .library import for_head_dim
+def _prefill_args(q, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, tiles, n_tokens, out):
     _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
     if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim):
         raise KernelError(f"cache pool must be [pages, {n_kv_heads}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
@@ -309,10 +306,40 @@ def attention_prefill(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: 
     if out is None:
         out = torch.empty(n_tokens, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
     _need(out, "out", torch.bfloat16, (n_tokens, n_heads * head_dim))
+    return out
+
+
+def attention_prefill(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
+                      tiles: torch.Tensor, n_tokens: int, window: Optional[int], scale: float,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention (bfloat16) of the token runs ``tiles`` (of at most 64 tokens) over the cache:
+    the mma.sync kernel, which takes every head size."""
+    from .library import for_head_dim
+    out = _prefill_args(q, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, tiles, n_tokens, out)
     check(for_head_dim(head_dim).pe_attention_prefill(
         q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
         table_stride, tiles.data_ptr(), None, None, tiles.shape[0], n_heads, n_kv_heads, head_dim, window or 0,
         float(scale), stream_ptr()), "attention_prefill")
+    return out
+
+
+def attention_prefill_tcgen05_takes(head_dim: int, scale: float) -> bool:
+    return head_dim in TCGEN05_HEAD_DIMS and scale > 0
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                              k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
+                              tiles: torch.Tensor, n_tokens: int, window: Optional[int], scale: float,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same on the tcgen05 tensor cores, for head sizes 64 and 128 and runs ``tiles`` of at most
+    128 tokens.  ``q`` is a view of ``n_tokens`` rows, ``q_stride`` elements apart."""
+    from .library import for_head_dim
+    out = _prefill_args(q, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, tiles, n_tokens, out)
+    check(for_head_dim(head_dim).pe_attention_prefill_tcgen05(
+        q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], block_table.data_ptr(),
+        table_stride, tiles.data_ptr(), tiles.shape[0], n_tokens, n_heads, n_kv_heads, head_dim, window or 0,
+        float(scale), status_word(q.device).data_ptr(), stream_ptr()), "attention_prefill_tcgen05")
     return out
 
 
@@ -326,11 +353,15 @@ def attention(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, hea
         if ctx.one_token_each:
             return attention_decode(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table,
                                     table_stride, tok_pos, tok_row, window, scale, ctx.max_context)
-        tiles = ctx.scratch.get("prefill_tiles")
+        tcgen05 = attention_prefill_tcgen05_takes(head_dim, scale)
+        name = "prefill_tiles_128" if tcgen05 else "prefill_tiles"
+        tiles = ctx.scratch.get(name)
         if tiles is None:
-            tiles = ctx.scratch["prefill_tiles"] = prefill_tiles(ctx.lens, ctx.starts, q.device)
-        return attention_prefill(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table,
-                                 table_stride, tiles, tok_pos.shape[0], window, scale)
+            tiles = ctx.scratch[name] = prefill_tiles(ctx.lens, ctx.starts, q.device,
+                                                      PREFILL_TILE_TCGEN05 if tcgen05 else PREFILL_TILE)
+        run = attention_prefill_tcgen05 if tcgen05 else attention_prefill
+        return run(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, table_stride, tiles,
+                   tok_pos.shape[0], window, scale)
     return attention_generic(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, table_stride,
                              tok_pos, tok_row, window, scale)
 

@@ -13,7 +13,7 @@ P, I, F, LL, ULL = c_void_p, c_int, c_float, c_longlong, c_ulonglong
 
 CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_mma.cu",
                 "linear_fused.cu", "gemm_tcgen05.cu")
-HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu")      # compiled per head size
+HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
     "pe_embed": [P, I, P, P, I, I, I, P],
@@ -39,6 +39,7 @@ _HEAD_DIM_SIGNATURES = {
     "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, P, P],
     "pe_attention_decode_splits": [I, I, I, I, P],
     "pe_attention_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
+    "pe_attention_prefill_tcgen05": [P, I, P, P, P, LL, P, I, P, I, I, I, I, I, I, F, P, P],
 }
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}

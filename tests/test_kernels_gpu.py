@@ -238,6 +238,39 @@ def test_attention_prefill(K, nh, nkv, hd, lens, window, cached):
     assert float(err.max()) < 2e-2, (float(err.max()), int(err.argmax()), tok_row[int(err.argmax())], tok_pos[int(err.argmax())])
 
 
+TCGEN05_CASES = [  # nh, nkv, hd, lens, window
+    (14, 2, 64, [300, 65], None),
+    (5, 1, 128, [130, 40], 64),
+    (3, 3, 64, [1, 128, 129, 7], None),       # runs of exactly one tile, one token more, and of a single token
+    (4, 2, 64, [700], 100),                   # a window that leaves whole pages behind inside a run's range
+    (2, 1, 128, [1000, 333], None),           # the ring of pages wraps many times
+    (6, 2, 128, [400], 129),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,window", TCGEN05_CASES)
+@pytest.mark.parametrize("cached", [0, 37])
+def test_attention_prefill_tcgen05(K, nh, nkv, hd, lens, window, cached):
+    """The tcgen05 kernel (runs of 128 tokens, S and O in tensor memory), with q as a strided view
+    of a wider matrix, as the engine hands it over."""
+    paged = Paged(lens, nkv, hd, torch.bfloat16, seed=hd + 4)
+    starts = [min(cached, n - 1) for n in lens]
+    step_lens = [n - s for n, s in zip(lens, starts)]
+    tok_row = [b for b, n in enumerate(step_lens) for _ in range(n)]
+    tok_pos = [s + i for s, n in zip(starts, step_lens) for i in range(n)]
+    q = bf(rnd(len(tok_row), nh, hd, seed=6))
+    kp, vp, table = paged.cuda()
+    wide = torch.zeros(len(tok_row), (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device="cuda")
+    wide[:, :nh * hd] = dev(q.reshape(len(tok_row), -1).to(torch.bfloat16))
+    tiles = K.prefill_tiles(step_lens, starts, "cuda", K.PREFILL_TILE_TCGEN05)
+    got = K.attention_prefill_tcgen05(wide, wide.shape[1], nh, nkv, hd, kp, vp, table, table.shape[1], tiles,
+                                      len(tok_row), window, hd ** -0.5)
+    K.check_status("cuda")
+    want = reference_attention(q, paged, tok_row, tok_pos, nh, window)
+    err = (got.float().cpu() - want).abs().max(dim=1).values
+    assert float(err.max()) < 2e-2, (float(err.max()), int(err.argmax()), tok_row[int(err.argmax())], tok_pos[int(err.argmax())])
+
+
 @pytest.mark.parametrize("kernel", ["generic_f32", "generic_bf16", "decode", "prefill"])
 def test_attention_finds_a_far_key_and_respects_the_windows_edge(K, kernel):
     """One key among hundreds is made to dominate.  Without a window the output must be its
