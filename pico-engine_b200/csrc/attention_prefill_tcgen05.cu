@@ -3,15 +3,19 @@
 // attention run as tcgen05.mma with their accumulators in tensor memory.
 //
 //   one CTA   = a run of up to 128 consecutive tokens of one sequence x one query head
+//   a step    = two pages of the cache (128 keys): products this small cost the tensor core more in
+//               fixed latency than in work, so fewer and larger ones are issued
 //   warp 0      loader: TMA tiled loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the run's
-//               queries and, page after page of the cache, of 64 keys and 64 values into a ring
-//   warp 1      allocates tensor memory; one lane issues S = Q.K^T (128 x 64, K = head size) into
-//               one of two S buffers and O += P.V (128 x head size, K = 64 keys): S of the next
-//               page is issued before P.V of this one, so the softmax never waits for the product
-//   warps 2-5   softmax, one thread a query row: tcgen05.ld of the row's 64 scores, mask, running
-//               maximum and sum in float32, P = 2^(s - max) rounded to bfloat16 into a swizzled
-//               shared-memory tile that is the A operand of P.V; when a row's maximum grows, the
-//               row of O in tensor memory is rescaled (tcgen05.ld / tcgen05.st) before P.V runs
+//               queries and, step after step, of the pages' keys and values into a ring; it alone
+//               reads the page table and tells the others through flags which pages are there
+//   warp 1      allocates tensor memory; one lane issues S = Q.K^T (128 x 128, K = head size) into
+//               one of two S buffers and O += P.V (128 x head size, K = 128 keys): S of the next
+//               step is issued before P.V of this one, so the softmax never waits for the product
+//   warps 2-5   softmax, one thread a query row, two passes over the row's 128 scores in tensor
+//               memory (tcgen05.ld is cheap, registers are not): the maximum; then P = 2^(s - max)
+//               rounded to bfloat16 into one of two swizzled shared-memory tiles, the A operand of
+//               P.V, and the row sum in float32; when a row's maximum grows, the row of O in tensor
+//               memory is rescaled (tcgen05.ld / tcgen05.st) before P.V runs
 //
 // Values lie in the cache as [key][head size], which is the MN-major form of the B operand of
 // P.V: its shared-memory descriptor steps 8 keys by 1024 bytes and 64 columns by one panel.
@@ -32,18 +36,22 @@
 #define AT_QTILE 128
 #define AT_KTILE PE_PAGE
 #define AT_PANELS (AT_HD / 64)                     // 64-column panels of a row: one 128-byte swizzle atom each
-#define AT_STAGES 3
+#define AT_STAGES (AT_HD == 64 ? 3 : 2)            // steps in flight or in use; a step is two pages (128 keys)
 #define AT_THREADS 192
 #define AT_WAIT_CYCLES 1000000000ll
 #define AT_Q_BYTES (AT_QTILE * AT_HD * 2)
-#define AT_PAGE_BYTES (AT_KTILE * AT_HD * 2)       // keys (or values) of one page and head
-#define AT_P_BYTES (AT_QTILE * AT_KTILE * 2)
-#define AT_TMEM_COLS 256                           // S buffers at columns 0 and 64, O from column 128
-#define AT_O_COL 128
+#define AT_STAGE_BYTES (2 * 2 * AT_KTILE * AT_HD * 2)   // keys, then values, of two pages and one head
+#define AT_P_BYTES (AT_QTILE * 2 * AT_KTILE * 2)   // P of one step: the A operand of P.V, two panels of 64 keys
+#define AT_TILE_BYTES (AT_Q_BYTES + AT_STAGES * AT_STAGE_BYTES + 2 * AT_P_BYTES)
+#define AT_SMEM_BYTES (AT_TILE_BYTES + 8 * (9 + 2 * AT_STAGES) + 4 * AT_STAGES)
+#define AT_TMEM_COLS 512                           // S buffers at columns 0 and 128, O from column 256
+#define AT_O_COL 256
+#define AT_LAZY 8.0f
 
 struct AtArgs {
     bf16* out; const int* block_table; int table_stride; const int4* tiles;
     int nh, nkv, window; float scale_log2e;
+    int pool_rows;                                 // rows of the key (and value) pool seen as a matrix [rows][head size]
 };
 
 __device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -81,7 +89,26 @@ __device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long a, un
 __device__ __forceinline__ void at_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void at_ld32(unsigned taddr, float* v) {     // 32 columns of this thread's lane; no wait
+// 32 columns of this thread's lane.  at_ld32_start only issues the load: the values are there after at_ld_wait, and
+// at_pin32 after that keeps the compiler from using the registers any earlier.
+__device__ __forceinline__ void at_ld32_start(unsigned taddr, unsigned* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void at_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void at_pin32(unsigned* r) {
+    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                      "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                      "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                      "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
+__device__ __forceinline__ void at_ld32(unsigned taddr, float* v) {     // load and wait
     unsigned r[32];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
                  "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -119,27 +146,35 @@ __device__ __forceinline__ unsigned at_pack(float lo, float hi) {
 }
 
 // tiles[i] = (batch row, first packed token, number of tokens (<= AT_QTILE), position of the first token)
-__global__ void __launch_bounds__(AT_THREADS, AT_HD == 64 ? 2 : 1) attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
-                                                                               const __grid_constant__ CUtensorMap map_k,
-                                                                               const __grid_constant__ CUtensorMap map_v,
-                                                                               const AtArgs p, int* status) {
-    extern __shared__ __align__(1024) unsigned char at_mem[];   // Q | stages of (K page, V page) | two P tiles
-    __shared__ __align__(8) unsigned long long q_full, kv_full[AT_STAGES], kv_empty[AT_STAGES], s_full[2], s_free[2], p_full[2], pv_done[2];
-    __shared__ unsigned tmem_base_s;
+__global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                                  const __grid_constant__ CUtensorMap map_k,
+                                                                                  const __grid_constant__ CUtensorMap map_v,
+                                                                                  const AtArgs p, int* status) {
+    // Q | stages of (K, V of two pages) | two P tiles | barriers and the stages' flags.  The tiles need 1024-byte
+    // alignment for the swizzle, which the declaration asks for and the kernel checks.
+    extern __shared__ __align__(1024) unsigned char at_mem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const unsigned base = (at_smem(at_mem) + 1023u) & ~1023u;
-    const unsigned q_s = base, kv_s = q_s + AT_Q_BYTES, p_s = kv_s + AT_STAGES * 2 * AT_PAGE_BYTES;
+    const unsigned q_s = at_smem(at_mem), kv_s = q_s + AT_Q_BYTES, p_s = kv_s + AT_STAGES * AT_STAGE_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(at_mem + AT_TILE_BYTES);
+    unsigned long long &q_full = bars[0], &p_full = bars[1];
+    unsigned long long *pv_done = bars + 2, *s_full = bars + 4, *s_free = bars + 6, *kv_full = bars + 8, *kv_empty = bars + 8 + AT_STAGES;
+    unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(bars + 8 + 2 * AT_STAGES);
+    volatile unsigned* stage_flags = reinterpret_cast<volatile unsigned*>(bars + 9 + 2 * AT_STAGES);   // bit g: page g of the stage exists
+    if (q_s & 1023u) {                                              // every thread alike: nothing is allocated yet
+        if (threadIdx.x == 0) atomicExch(status, 6);
+        return;
+    }
 
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&q_full)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(at_smem(&p_full)) : "memory");          // the four softmax warps
         for (int s = 0; s < AT_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&kv_full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&kv_empty[s])) : "memory");
         }
         for (int b = 0; b < 2; ++b) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&s_full[b])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(at_smem(&s_free[b])) : "memory");   // the four softmax warps
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(at_smem(&p_full[b])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(at_smem(&s_free[b])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&pv_done[b])) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,74 +192,82 @@ __global__ void __launch_bounds__(AT_THREADS, AT_HD == 64 ? 2 : 1) attention_pre
     pdl_launch_dependents();
     pdl_wait();
 
-    const int4 info = p.tiles[blockIdx.x];
+    const int4 info = p.tiles[blockIdx.y];                          // heads vary fastest: the runs that see the most keys start first
     const int brow = info.x, tok0 = info.y, n = info.z, pos0 = info.w;
-    const int h = blockIdx.y, kvh = h / (p.nh / p.nkv);
-    const int* table = p.block_table + (size_t)brow * p.table_stride;
-    // the pages the run can see: from the first row's window start to the last row's position;
-    // pages that the window has left behind have no physical page any more and are skipped by every role alike
+    const int h = blockIdx.x, kvh = h / (p.nh / p.nkv);
+    // the pages the run can see: from the first row's window start to the last row's position, two to a step
     const int first_key = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
     const int page_lo = first_key / AT_KTILE, page_hi = (pos0 + n - 1) / AT_KTILE;
+    const int n_steps = (page_hi - page_lo + 2) / 2;
 
     if (warp == 0) {
         if (lane == 0) {                                            // ---------------- loader
+            const int* table = p.block_table + (size_t)brow * p.table_stride;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(&q_full)), "r"((unsigned)AT_Q_BYTES) : "memory");
 #pragma unroll
             for (int c = 0; c < AT_PANELS; ++c) at_tma_2d(q_s + c * (AT_QTILE * 128), &map_q, h * AT_HD + 64 * c, tok0, at_smem(&q_full));
-            int j = 0;
-            for (int pi = page_lo; pi <= page_hi; ++pi) {
-                const int page = table[pi];
-                if (page < 0) continue;
-                const int s = j % AT_STAGES;
-                if (j >= AT_STAGES && !at_wait(at_smem(&kv_empty[s]), (unsigned)((j / AT_STAGES) - 1) & 1u)) { atomicExch(status, 5); break; }
-                const unsigned bar = at_smem(&kv_full[s]), k_dst = kv_s + s * 2 * AT_PAGE_BYTES, v_dst = k_dst + AT_PAGE_BYTES;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)(2 * AT_PAGE_BYTES)) : "memory");
-                const int y = (page * p.nkv + kvh) * AT_KTILE;
+            int page[2] = {table[page_lo], page_lo + 1 <= page_hi ? table[page_lo + 1] : -1};
+            for (int it = 0; it < n_steps; ++it) {
+                const int s = it % AT_STAGES;
+                int next[2] = {-1, -1};                             // the step after this one: its entries travel during the wait
+                if (page_lo + 2 * it + 2 <= page_hi) next[0] = table[page_lo + 2 * it + 2];
+                if (page_lo + 2 * it + 3 <= page_hi) next[1] = table[page_lo + 2 * it + 3];
+                if (it >= AT_STAGES && !at_wait(at_smem(&kv_empty[s]), (unsigned)((it / AT_STAGES) - 1) & 1u)) { atomicExch(status, 5); break; }
+                const unsigned bar = at_smem(&kv_full[s]), k_dst = kv_s + s * AT_STAGE_BYTES, v_dst = k_dst + AT_STAGE_BYTES / 2;
+                stage_flags[s] = (page[0] >= 0 ? 1u : 0u) | (page[1] >= 0 ? 2u : 0u);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)AT_STAGE_BYTES) : "memory");
 #pragma unroll
-                for (int c = 0; c < AT_PANELS; ++c) {
-                    at_tma_2d(k_dst + c * (AT_KTILE * 128), &map_k, 64 * c, y, bar);
-                    at_tma_2d(v_dst + c * (AT_KTILE * 128), &map_v, 64 * c, y, bar);
+                for (int g = 0; g < 2; ++g) {
+                    // a page that is not there (beyond the run's last page, or left behind by the window) is read from
+                    // beyond the pool's end, which gives zeros: its scores are masked and its values add nothing
+                    const int y = page[g] >= 0 ? (page[g] * p.nkv + kvh) * AT_KTILE : p.pool_rows;
+#pragma unroll
+                    for (int c = 0; c < AT_PANELS; ++c) {
+                        at_tma_2d(k_dst + c * (2 * AT_KTILE * 128) + g * (AT_KTILE * 128), &map_k, 64 * c, y, bar);
+                        at_tma_2d(v_dst + c * (2 * AT_KTILE * 128) + g * (AT_KTILE * 128), &map_v, 64 * c, y, bar);
+                    }
                 }
-                ++j;
+                page[0] = next[0]; page[1] = next[1];
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {                                            // ---------------- MMA issuer
             // instruction descriptors: float32 accumulator, bfloat16 operands, M = 128;
-            // S: A and B K-major, N = 64 keys;  O: B MN-major (bit 16), N = head size
-            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_KTILE >> 3) << 17) | ((unsigned)(AT_QTILE >> 4) << 24);
+            // S: A and B K-major, N = 128 keys;  O: B MN-major (bit 16), N = head size
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)((2 * AT_KTILE) >> 3) << 17) | ((unsigned)(AT_QTILE >> 4) << 24);
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(AT_HD >> 3) << 17) | ((unsigned)(AT_QTILE >> 4) << 24);
-            int n_pages = 0;
-            for (int pi = page_lo; pi <= page_hi; ++pi) n_pages += table[pi] >= 0;
+            // operand descriptors of stage 0 and P tile 0; a stage or tile further on adds its offset in 16-byte units
+            const unsigned long long dq = at_desc(q_s, 0, 1024), dk = at_desc(kv_s, 0, 1024), dp = at_desc(p_s, 0, 1024);
+            const unsigned long long dv = at_desc(kv_s + AT_STAGE_BYTES / 2, 2 * AT_KTILE * 128, 1024);
             bool ok = at_wait(at_smem(&q_full), 0u);
-            auto issue_s = [&](int j) -> bool {                     // S_j = Q . K_j^T into S buffer j & 1
-                const int s = j % AT_STAGES, b = j & 1;
-                if (!at_wait(at_smem(&kv_full[s]), (unsigned)(j / AT_STAGES) & 1u)) return false;
-                if (j >= 2 && !at_wait(at_smem(&s_free[b]), (unsigned)((j >> 1) - 1) & 1u)) return false;
+            auto issue_s = [&](int it) -> bool {                    // S = Q . K^T of step `it` into S buffer it & 1
+                const int s = it % AT_STAGES, b = it & 1;
+                if (!at_wait(at_smem(&kv_full[s]), (unsigned)(it / AT_STAGES) & 1u)) return false;
+                if (it >= 2 && !at_wait(at_smem(&s_free[b]), (unsigned)((it >> 1) - 1) & 1u)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned k_src = kv_s + s * 2 * AT_PAGE_BYTES;
+                const unsigned long long dks = dk + (unsigned long long)(s * (AT_STAGE_BYTES >> 4));
 #pragma unroll
-                for (int kk = 0; kk < AT_HD / 16; ++kk) {
-                    const unsigned panel = kk / 4, in = (kk % 4) * 32;   // 16 columns = 32 bytes inside the swizzle atom
-                    at_mma(tmem + b * AT_KTILE, at_desc(q_s + panel * (AT_QTILE * 128) + in, 0, 1024),
-                           at_desc(k_src + panel * (AT_KTILE * 128) + in, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < AT_HD / 16; ++kk) {           // 16 columns = 32 bytes inside the swizzle atom; 64 columns = one panel
+                    const unsigned off_q = ((kk / 4) * (AT_QTILE * 128) + (kk % 4) * 32) >> 4, off_k = ((kk / 4) * (2 * AT_KTILE * 128) + (kk % 4) * 32) >> 4;
+                    at_mma(tmem + b * (2 * AT_KTILE), dq + off_q, dks + off_k, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 at_commit(at_smem(&s_full[b]));
                 return true;
             };
-            if (ok && n_pages > 0) ok = issue_s(0);
-            for (int j = 0; j < n_pages && ok; ++j) {
-                if (j + 1 < n_pages && !issue_s(j + 1)) { ok = false; break; }
-                const int s = j % AT_STAGES, b = j & 1;
-                if (!at_wait(at_smem(&p_full[b]), (unsigned)(j >> 1) & 1u)) { ok = false; break; }
+            if (ok) ok = issue_s(0);
+            for (int it = 0; it < n_steps && ok; ++it) {
+                if (it + 1 < n_steps && !issue_s(it + 1)) { ok = false; break; }
+                const int s = it % AT_STAGES, b = it & 1;
+                if (!at_wait(at_smem(&p_full), (unsigned)it & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned v_src = kv_s + s * 2 * AT_PAGE_BYTES + AT_PAGE_BYTES, p_src = p_s + b * AT_P_BYTES;
+                const unsigned long long dps = dp + (unsigned long long)(b * (AT_P_BYTES >> 4)), dvs = dv + (unsigned long long)(s * (AT_STAGE_BYTES >> 4));
 #pragma unroll
-                for (int kk = 0; kk < AT_KTILE / 16; ++kk)          // 16 keys: 32 bytes further in P's rows, 16 rows further in V
-                    at_mma(tmem + AT_O_COL, at_desc(p_src + kk * 32, 0, 1024),
-                           at_desc(v_src + kk * 16 * 128, AT_KTILE * 128, 1024), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 2 * AT_KTILE / 16; ++kk) {    // 16 keys: 32 bytes further in P's rows (64 keys a panel), 16 rows further in V
+                    const unsigned off_p = ((kk / 4) * (AT_QTILE * 128) + (kk % 4) * 32) >> 4, off_v = (kk * 16 * 128) >> 4;
+                    at_mma(tmem + AT_O_COL, dps + off_p, dvs + off_v, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+                }
                 at_commit(at_smem(&kv_empty[s]));                   // the stage's keys and values have been read
-                at_commit(at_smem(&pv_done[b]));                    // and O holds this page's share
+                at_commit(at_smem(&pv_done[b]));                    // and O holds this step's share
             }
             if (!ok) atomicExch(status, 5);
         }
@@ -235,37 +278,55 @@ __global__ void __launch_bounds__(AT_THREADS, AT_HD == 64 ? 2 : 1) attention_pre
         const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        int j = 0;
-        for (int pi = page_lo; pi <= page_hi && ok; ++pi) {
-            if (table[pi] < 0) continue;
-            const int b = j & 1;
-            if (!at_wait_warp(at_smem(&s_full[b]), (unsigned)(j >> 1) & 1u)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float s[AT_KTILE];
-            at_ld32(lane_addr + b * AT_KTILE, s);
-            at_ld32(lane_addr + b * AT_KTILE + 32, s + 32);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) at_arrive(at_smem(&s_free[b]));          // the buffer may take S of the page after next
-            const int key0 = pi * AT_KTILE;
-            const bool whole = key0 + AT_KTILE - 1 <= p_r && (p.window <= 0 || key0 > p_r - p.window);
+        int it = 0;
+        // 64 scores of this thread's row, masked: the keys from key0 on, of which the row sees those up to its own
+        // position and inside its window
+        auto load_scores = [&](unsigned taddr, int key0, bool there, float* s) {
+            unsigned raw[AT_KTILE];
+            at_ld32_start(taddr, raw);
+            at_ld32_start(taddr + 32, raw + 32);
+            at_ld_wait();
+            at_pin32(raw); at_pin32(raw + 32);
+#pragma unroll
+            for (int c = 0; c < AT_KTILE; ++c) s[c] = __uint_as_float(raw[c]);
+            const bool whole = there && key0 + AT_KTILE - 1 <= p_r && (p.window <= 0 || key0 > p_r - p.window);
             if (!whole) {
 #pragma unroll
                 for (int c = 0; c < AT_KTILE; ++c) {
                     const int key = key0 + c;
-                    if (key > p_r || (p.window > 0 && key <= p_r - p.window)) s[c] = -INFINITY;
+                    if (!there || key > p_r || (p.window > 0 && key <= p_r - p.window)) s[c] = -INFINITY;
                 }
             }
-            float m_tile = s[0];
+        };
+        for (; it < n_steps; ++it) {
+            const int b = it & 1, st = it % AT_STAGES;
+            if (!at_wait_warp(at_smem(&kv_full[st]), (unsigned)(it / AT_STAGES) & 1u)) { ok = false; break; }   // the loader's flags
+            const unsigned flags = stage_flags[st];
+            if (!at_wait_warp(at_smem(&s_full[b]), (unsigned)(it >> 1) & 1u)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int key0 = (page_lo + 2 * it) * AT_KTILE;
+            const unsigned s_addr = lane_addr + b * (2 * AT_KTILE);
+            // first pass: the row's maximum over the step's 128 scores
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: a warp has little else to hide their latency
+#pragma unroll 1                                                    // one copy of the code: the loop is bound by instruction fetch as it is
+            for (int g = 0; g < 2; ++g) {
+                float s[AT_KTILE];
+                load_scores(s_addr + g * AT_KTILE, key0 + g * AT_KTILE, (flags >> g) & 1u, s);
 #pragma unroll
-            for (int c = 1; c < AT_KTILE; ++c) m_tile = fmaxf(m_tile, s[c]);
-            const float m_new = fmaxf(m_run, m_tile * p.scale_log2e);
+                for (int c = 0; c < AT_KTILE; ++c) mx[c & 3] = fmaxf(mx[c & 3], s[c]);
+            }
+            // The reference point of the exponentials follows the row's maximum only when that has grown by more than
+            // AT_LAZY (in powers of two): P then holds values up to 2^AT_LAZY, which bfloat16 and the float32 sums take
+            // as well as values up to 1, and O is rescaled on few steps instead of on nearly all.
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e;
+            const float m_new = (m_run != -INFINITY && m_tile <= m_run + AT_LAZY) ? m_run : fmaxf(m_run, m_tile);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = m_run == -INFINITY ? (l_run = 0.f, 1.0f) : at_exp2(m_run - m_use);
-            // P's buffer is free once P.V of the page before last is done
-            if (j >= 2 && !at_wait_warp(at_smem(&pv_done[b]), (unsigned)((j - 2) >> 1) & 1u)) { ok = false; break; }
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {  // a row's maximum grew: rescale the warp's rows of O
-                if (!at_wait_warp(at_smem(&pv_done[(j - 1) & 1]), (unsigned)((j - 1) >> 1) & 1u)) { ok = false; break; }
+            const float alpha = m_run == -INFINITY ? 1.0f : at_exp2(m_run - m_use);
+            m_run = m_new;
+            // this P tile is free once P.V of the step before last is done
+            if (it >= 2 && !at_wait_warp(at_smem(&pv_done[b]), (unsigned)((it >> 1) - 1) & 1u)) { ok = false; break; }
+            if (it > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) { // a row's maximum grew: rescale the warp's rows of O
+                if (!at_wait_warp(at_smem(&pv_done[b ^ 1]), (unsigned)((it - 1) >> 1) & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                 for (int c = 0; c < AT_HD; c += 32) {
@@ -277,27 +338,39 @@ __global__ void __launch_bounds__(AT_THREADS, AT_HD == 64 ? 2 : 1) attention_pre
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            m_run = m_new;
-            float sum = 0.f;
-            unsigned char* p_row = at_mem + (p_s - at_smem(at_mem)) + b * AT_P_BYTES + r * 128;
+            // second pass: P = 2^(s - max), its row sum, and the bfloat16 tile for P.V (a panel of 64 keys = 128 bytes a row)
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            unsigned char* p_row = at_mem + (p_s - q_s) + b * AT_P_BYTES + r * 128;
+#pragma unroll 1
+            for (int g = 0; g < 2; ++g) {
+                float s[AT_KTILE];
+                load_scores(s_addr + g * AT_KTILE, key0 + g * AT_KTILE, (flags >> g) & 1u, s);
+                if (g == 1) {                                       // S has been read for the last time
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) at_arrive(at_smem(&s_free[b]));
+                }
+                unsigned packed[AT_KTILE / 2];
 #pragma unroll
-            for (int c = 0; c < AT_KTILE; c += 8) {
-                float e[8];
+                for (int c = 0; c < AT_KTILE; c += 2) {
+                    const float e0 = at_exp2(fmaf(s[c], p.scale_log2e, -m_use)), e1 = at_exp2(fmaf(s[c + 1], p.scale_log2e, -m_use));
+                    sum[c & 3] += e0; sum[(c + 1) & 3] += e1;
+                    packed[c >> 1] = at_pack(e0, e1);
+                }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = at_exp2(fmaf(s[c + i], p.scale_log2e, -m_use)); sum += e[i]; }
-                *reinterpret_cast<uint4*>(p_row + ((((c >> 3) ^ (r & 7))) << 4)) =
-                    make_uint4(at_pack(e[0], e[1]), at_pack(e[2], e[3]), at_pack(e[4], e[5]), at_pack(e[6], e[7]));
+                for (int c = 0; c < AT_KTILE / 8; ++c)
+                    *reinterpret_cast<uint4*>(p_row + g * (AT_QTILE * 128) + ((c ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) at_arrive(at_smem(&p_full[b]));
-            ++j;
+            if (lane == 0) at_arrive(at_smem(&p_full));
         }
         // the last P.V (products complete in the order they were issued)
-        if (ok && j > 0 && !at_wait_warp(at_smem(&pv_done[(j - 1) & 1]), (unsigned)((j - 1) >> 1) & 1u)) ok = false;
-        if (ok && j > 0) {
+        if (ok && it > 0 && !at_wait_warp(at_smem(&pv_done[(it - 1) & 1]), (unsigned)((it - 1) >> 1) & 1u)) ok = false;
+        if (ok && it > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             bf16* o_row = p.out + ((size_t)(tok0 + r) * p.nh + h) * AT_HD;
@@ -359,15 +432,23 @@ int at_make_map(CUtensorMap* map, const void* base, long long rows, long long co
 
 extern "C" int pe_attention_prefill_tcgen05_tile() { return AT_QTILE; }
 
+// how many of the kernel's CTAs an SM holds at once (2 at head size 64, 1 at 128), or a negative CUDA error
+extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() {
+    int n = 0;
+    if (cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM_BYTES) != cudaSuccess) return -1;
+    const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_prefill_tcgen05_kernel, AT_THREADS, AT_SMEM_BYTES);
+    return e == cudaSuccess ? n : -(int)e;
+}
+
 // q: [n_tokens][q_stride] with head h at columns h * hd; pools: [pool_pages][nkv][64][hd]
 extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                             long long pool_pages, const int* block_table, int table_stride, const void* tiles,
                                             int n_tiles, int n_tokens, int nh, int nkv, int hd, int window, float scale,
                                             int* status, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (hd != AT_HD || nkv <= 0 || nh % nkv || nh > 65535 || q_stride % 8 || !(scale > 0.f) || !status) return PE_ERR_UNSUPPORTED;
+    if (hd != AT_HD || nkv <= 0 || nh % nkv || n_tiles > 65535 || q_stride % 8 || !(scale > 0.f) || !status) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out | (uintptr_t)tiles) & 15) return PE_ERR_UNSUPPORTED;
-    if (pool_pages * nkv * AT_KTILE > 0x7fffffffll) return PE_ERR_UNSUPPORTED;       // TMA coordinates are 32-bit
+    if (pool_pages * nkv * AT_KTILE > 0x7fffff00ll) return PE_ERR_UNSUPPORTED;       // TMA coordinates are 32-bit
     CUtensorMap mq, mk, mv;
     int rc = at_make_map(&mq, q, n_tokens, (long long)nh * hd, q_stride, AT_QTILE);
     if (rc) return rc;
@@ -378,19 +459,21 @@ extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* o
     AtArgs p = {};
     p.out = (bf16*)out; p.block_table = block_table; p.table_stride = table_stride; p.tiles = (const int4*)tiles;
     p.nh = nh; p.nkv = nkv; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)AT_Q_BYTES + AT_STAGES * 2 * AT_PAGE_BYTES + 2 * AT_P_BYTES + 1024;
+    p.pool_rows = (int)(pool_pages * nkv * AT_KTILE);
+    const size_t smem = AT_SMEM_BYTES;
     static bool attr_set = false;
     if (!attr_set) {
         PE_TRY(cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    PE_TRY(pe_launch(attention_prefill_tcgen05_kernel, dim3(n_tiles, nh), AT_THREADS, smem, (cudaStream_t)stream, mq, mk, mv, p, status));
+    PE_TRY(pe_launch(attention_prefill_tcgen05_kernel, dim3(nh, n_tiles), AT_THREADS, smem, (cudaStream_t)stream, mq, mk, mv, p, status));
     return 0;
 }
 
 #else   // other head sizes: the mma.sync kernel of attention_prefill.cu takes them
 
 extern "C" int pe_attention_prefill_tcgen05_tile() { return 0; }
+extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() { return 0; }
 extern "C" int pe_attention_prefill_tcgen05(const void*, int, void*, const void*, const void*, long long, const int*, int, const void*,
                                             int, int, int, int, int, int, float, int*, void*) {
     return PE_ERR_UNSUPPORTED;
