@@ -11,11 +11,14 @@
 //   warp 1      allocates tensor memory; one lane issues S = Q.K^T (128 x 128, K = head size) into
 //               one of two S buffers and O += P.V (128 x head size, K = 128 keys): S of the next
 //               step is issued before P.V of this one, so the softmax never waits for the product
-//   warps 2-5   softmax, one thread a query row, two passes over the row's 128 scores in tensor
-//               memory (tcgen05.ld is cheap, registers are not): the maximum; then P = 2^(s - max)
-//               rounded to bfloat16 into one of two swizzled shared-memory tiles, the A operand of
-//               P.V, and the row sum in float32; when a row's maximum grows, the row of O in tensor
-//               memory is rescaled (tcgen05.ld / tcgen05.st) before P.V runs
+//   warps 2-9   softmax, two threads a query row, one for each page of the step: tcgen05.ld of its
+//               64 scores, mask, maximum (the two tell each other theirs through shared memory),
+//               P = 2^(s - max) rounded to bfloat16 into one of two swizzled shared-memory tiles,
+//               the A operand of P.V, and the row sum in float32; when a row's reference point
+//               moves, the row of O in tensor memory is rescaled (tcgen05.ld / tcgen05.st), each
+//               thread its half, before P.V runs.  Two warps on each of the SM's four schedulers
+//               hide each other's latencies; the exponentials (one special-function unit a
+//               scheduler) and the tensor core's time for the two products then bound a step.
 //
 // Values lie in the cache as [key][head size], which is the MN-major form of the B operand of
 // P.V: its shared-memory descriptor steps 8 keys by 1024 bytes and 64 columns by one panel.
@@ -37,13 +40,14 @@
 #define AT_KTILE PE_PAGE
 #define AT_PANELS (AT_HD / 64)                     // 64-column panels of a row: one 128-byte swizzle atom each
 #define AT_STAGES (AT_HD == 64 ? 3 : 2)            // steps in flight or in use; a step is two pages (128 keys)
-#define AT_THREADS 192
+#define AT_THREADS 320                             // loader, MMA issuer, and two softmax warps for each 32 rows
 #define AT_WAIT_CYCLES 1000000000ll
 #define AT_Q_BYTES (AT_QTILE * AT_HD * 2)
 #define AT_STAGE_BYTES (2 * 2 * AT_KTILE * AT_HD * 2)   // keys, then values, of two pages and one head
 #define AT_P_BYTES (AT_QTILE * 2 * AT_KTILE * 2)   // P of one step: the A operand of P.V, two panels of 64 keys
 #define AT_TILE_BYTES (AT_Q_BYTES + AT_STAGES * AT_STAGE_BYTES + 2 * AT_P_BYTES)
-#define AT_SMEM_BYTES (AT_TILE_BYTES + 8 * (9 + 2 * AT_STAGES) + 4 * AT_STAGES)
+#define AT_BAR_WORDS (13 + 2 * AT_STAGES)
+#define AT_SMEM_BYTES (AT_TILE_BYTES + 8 * AT_BAR_WORDS + 8 * AT_STAGES + 2 * 2 * AT_QTILE * 4)
 #define AT_TMEM_COLS 512                           // S buffers at columns 0 and 128, O from column 256
 #define AT_O_COL 256
 #define AT_LAZY 8.0f
@@ -56,9 +60,12 @@ struct AtArgs {
 
 __device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool at_wait(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;                                          // the usual case costs neither a clock read nor a suspended wait
     const long long deadline = clock64() + AT_WAIT_CYCLES;
     for (;;) {
-        unsigned done;
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
@@ -158,8 +165,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(at_mem + AT_TILE_BYTES);
     unsigned long long &q_full = bars[0], &p_full = bars[1];
     unsigned long long *pv_done = bars + 2, *s_full = bars + 4, *s_free = bars + 6, *kv_full = bars + 8, *kv_empty = bars + 8 + AT_STAGES;
-    unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(bars + 8 + 2 * AT_STAGES);
-    volatile unsigned* stage_flags = reinterpret_cast<volatile unsigned*>(bars + 9 + 2 * AT_STAGES);   // bit g: page g of the stage exists
+    unsigned long long* pair_bar = bars + 8 + 2 * AT_STAGES;       // one for the two softmax warps of each 32 rows
+    unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(bars + 12 + 2 * AT_STAGES);
+    volatile unsigned* stage_flags = reinterpret_cast<volatile unsigned*>(bars + AT_BAR_WORDS);   // bit g: page g of the stage exists
+    float* exchange = reinterpret_cast<float*>(bars + AT_BAR_WORDS + AT_STAGES);    // [step parity][half][row]: what the halves of a row tell each other
     if (q_s & 1023u) {                                              // every thread alike: nothing is allocated yet
         if (threadIdx.x == 0) atomicExch(status, 6);
         return;
@@ -167,14 +176,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
 
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&q_full)) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(at_smem(&p_full)) : "memory");          // the four softmax warps
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(at_smem(&p_full)) : "memory");          // the eight softmax warps
+        for (int q = 0; q < 4; ++q) asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(at_smem(&pair_bar[q])) : "memory");
         for (int s = 0; s < AT_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&kv_full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&kv_empty[s])) : "memory");
         }
         for (int b = 0; b < 2; ++b) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&s_full[b])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(at_smem(&s_free[b])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(at_smem(&s_free[b])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&pv_done[b])) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -271,22 +281,47 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
             }
             if (!ok) atomicExch(status, 5);
         }
-    } else {                                                        // ---------------- softmax, warps 2..5
+    } else {                                                        // ---------------- softmax, warps 2..9
+        // Two threads a query row: thread (row, g) has the scores of the step's page g (64 keys) and half of the
+        // row of O.  The two tell each other their maxima, and at the end their sums, through shared memory.
         const int quarter = warp & 3;                               // the 32 lanes of tensor memory this warp may touch
+        const int g = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                          // this thread's query row
         const int p_r = pos0 + r;
         const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+        const unsigned o_addr = lane_addr + AT_O_COL + g * (AT_HD / 2);
+        const unsigned pair = at_smem(&pair_bar[quarter]);
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        int it = 0;
-        // 64 scores of this thread's row, masked: the keys from key0 on, of which the row sees those up to its own
-        // position and inside its window
-        auto load_scores = [&](unsigned taddr, int key0, bool there, float* s) {
+        int it = 0, met = 0;                                        // met: how often the row's two threads have met
+        // tell the other half `mine`, learn what it tells
+        auto swap = [&](float mine, float& theirs) -> bool {
+            float* slot = exchange + (met & 1) * (2 * AT_QTILE);
+            slot[g * AT_QTILE + r] = mine;
+            __syncwarp();
+            if (lane == 0) at_arrive(pair);
+            if (!at_wait_warp(pair, (unsigned)met & 1u)) return false;
+            theirs = slot[(g ^ 1) * AT_QTILE + r];
+            ++met;
+            return true;
+        };
+        for (; it < n_steps; ++it) {
+            const int b = it & 1, st = it % AT_STAGES;
+            if (!at_wait_warp(at_smem(&kv_full[st]), (unsigned)(it / AT_STAGES) & 1u)) { ok = false; break; }   // the loader's flags
+            const bool there = (stage_flags[st] >> g) & 1u;
+            if (!at_wait_warp(at_smem(&s_full[b]), (unsigned)(it >> 1) & 1u)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int key0 = (page_lo + 2 * it + g) * AT_KTILE;
             unsigned raw[AT_KTILE];
-            at_ld32_start(taddr, raw);
-            at_ld32_start(taddr + 32, raw + 32);
+            at_ld32_start(lane_addr + b * (2 * AT_KTILE) + g * AT_KTILE, raw);
+            at_ld32_start(lane_addr + b * (2 * AT_KTILE) + g * AT_KTILE + 32, raw + 32);
             at_ld_wait();
             at_pin32(raw); at_pin32(raw + 32);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) at_arrive(at_smem(&s_free[b]));          // the buffer may take S of the step after next
+            // the row sees the keys up to its own position and inside its window
+            float s[AT_KTILE];
 #pragma unroll
             for (int c = 0; c < AT_KTILE; ++c) s[c] = __uint_as_float(raw[c]);
             const bool whole = there && key0 + AT_KTILE - 1 <= p_r && (p.window <= 0 || key0 > p_r - p.window);
@@ -297,87 +332,68 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
                     if (!there || key > p_r || (p.window > 0 && key <= p_r - p.window)) s[c] = -INFINITY;
                 }
             }
-        };
-        for (; it < n_steps; ++it) {
-            const int b = it & 1, st = it % AT_STAGES;
-            if (!at_wait_warp(at_smem(&kv_full[st]), (unsigned)(it / AT_STAGES) & 1u)) { ok = false; break; }   // the loader's flags
-            const unsigned flags = stage_flags[st];
-            if (!at_wait_warp(at_smem(&s_full[b]), (unsigned)(it >> 1) & 1u)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int key0 = (page_lo + 2 * it) * AT_KTILE;
-            const unsigned s_addr = lane_addr + b * (2 * AT_KTILE);
-            // first pass: the row's maximum over the step's 128 scores
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: a warp has little else to hide their latency
-#pragma unroll 1                                                    // one copy of the code: the loop is bound by instruction fetch as it is
-            for (int g = 0; g < 2; ++g) {
-                float s[AT_KTILE];
-                load_scores(s_addr + g * AT_KTILE, key0 + g * AT_KTILE, (flags >> g) & 1u, s);
+            float mx[4] = {s[0], s[1], s[2], s[3]};                 // four chains: a warp has little else to hide their latency
 #pragma unroll
-                for (int c = 0; c < AT_KTILE; ++c) mx[c & 3] = fmaxf(mx[c & 3], s[c]);
-            }
+            for (int c = 4; c < AT_KTILE; ++c) mx[c & 3] = fmaxf(mx[c & 3], s[c]);
+            const float m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            float m_theirs;
+            if (!swap(m_mine, m_theirs)) { ok = false; break; }
             // The reference point of the exponentials follows the row's maximum only when that has grown by more than
             // AT_LAZY (in powers of two): P then holds values up to 2^AT_LAZY, which bfloat16 and the float32 sums take
-            // as well as values up to 1, and O is rescaled on few steps instead of on nearly all.
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e;
+            // as well as values up to 1, and O is rescaled on few steps instead of on nearly all.  Both threads of a
+            // row compute the same from the same numbers.
+            const float m_tile = fmaxf(m_mine, m_theirs) * p.scale_log2e;
             const float m_new = (m_run != -INFINITY && m_tile <= m_run + AT_LAZY) ? m_run : fmaxf(m_run, m_tile);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = m_run == -INFINITY ? 1.0f : at_exp2(m_run - m_use);
             m_run = m_new;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            unsigned packed[AT_KTILE / 2];
+#pragma unroll
+            for (int c = 0; c < AT_KTILE; c += 2) {
+                const float e0 = at_exp2(fmaf(s[c], p.scale_log2e, -m_use)), e1 = at_exp2(fmaf(s[c + 1], p.scale_log2e, -m_use));
+                sum[c & 3] += e0; sum[(c + 1) & 3] += e1;
+                packed[c >> 1] = at_pack(e0, e1);
+            }
+            l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
             // this P tile is free once P.V of the step before last is done
             if (it >= 2 && !at_wait_warp(at_smem(&pv_done[b]), (unsigned)((it >> 1) - 1) & 1u)) { ok = false; break; }
-            if (it > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) { // a row's maximum grew: rescale the warp's rows of O
+            if (it > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) { // a row's reference point moved: rescale this half of the warp's rows of O
                 if (!at_wait_warp(at_smem(&pv_done[b ^ 1]), (unsigned)((it - 1) >> 1) & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (int c = 0; c < AT_HD; c += 32) {
+                for (int c = 0; c < AT_HD / 2; c += 32) {
                     float o[32];
-                    at_ld32(lane_addr + AT_O_COL + c, o);
+                    at_ld32(o_addr + c, o);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                    at_st32(lane_addr + AT_O_COL + c, o);
+                    at_st32(o_addr + c, o);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // second pass: P = 2^(s - max), its row sum, and the bfloat16 tile for P.V (a panel of 64 keys = 128 bytes a row)
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-            unsigned char* p_row = at_mem + (p_s - q_s) + b * AT_P_BYTES + r * 128;
-#pragma unroll 1
-            for (int g = 0; g < 2; ++g) {
-                float s[AT_KTILE];
-                load_scores(s_addr + g * AT_KTILE, key0 + g * AT_KTILE, (flags >> g) & 1u, s);
-                if (g == 1) {                                       // S has been read for the last time
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) at_arrive(at_smem(&s_free[b]));
-                }
-                unsigned packed[AT_KTILE / 2];
+            // P as bfloat16 for P.V: panel g of the tile (64 keys = 128 bytes a row)
+            unsigned char* p_row = at_mem + (p_s - q_s) + b * AT_P_BYTES + g * (AT_QTILE * 128) + r * 128;
 #pragma unroll
-                for (int c = 0; c < AT_KTILE; c += 2) {
-                    const float e0 = at_exp2(fmaf(s[c], p.scale_log2e, -m_use)), e1 = at_exp2(fmaf(s[c + 1], p.scale_log2e, -m_use));
-                    sum[c & 3] += e0; sum[(c + 1) & 3] += e1;
-                    packed[c >> 1] = at_pack(e0, e1);
-                }
-#pragma unroll
-                for (int c = 0; c < AT_KTILE / 8; ++c)
-                    *reinterpret_cast<uint4*>(p_row + g * (AT_QTILE * 128) + ((c ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            }
-            l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+            for (int c = 0; c < AT_KTILE / 8; ++c)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) at_arrive(at_smem(&p_full));
         }
-        // the last P.V (products complete in the order they were issued)
+        // the row's sum, and the last P.V (products complete in the order they were issued)
+        float l_theirs = 0.f;
+        if (ok && !swap(l_run, l_theirs)) ok = false;
         if (ok && it > 0 && !at_wait_warp(at_smem(&pv_done[(it - 1) & 1]), (unsigned)((it - 1) >> 1) & 1u)) ok = false;
         if (ok && it > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* o_row = p.out + ((size_t)(tok0 + r) * p.nh + h) * AT_HD;
+            const float l = g == 0 ? l_run + l_theirs : l_theirs + l_run;   // the same sum in both threads
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* o_row = p.out + ((size_t)(tok0 + r) * p.nh + h) * AT_HD + g * (AT_HD / 2);
 #pragma unroll 1
-            for (int c = 0; c < AT_HD; c += 32) {
+            for (int c = 0; c < AT_HD / 2; c += 32) {
                 float o[32];
-                at_ld32(lane_addr + AT_O_COL + c, o);
+                at_ld32(o_addr + c, o);
                 if (r < n) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8)

@@ -271,11 +271,11 @@ def test_attention_prefill_tcgen05(K, nh, nkv, hd, lens, window, cached):
     assert float(err.max()) < 2e-2, (float(err.max()), int(err.argmax()), tok_row[int(err.argmax())], tok_pos[int(err.argmax())])
 
 
-@pytest.mark.parametrize("kernel", ["generic_f32", "generic_bf16", "decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["generic_f32", "generic_bf16", "decode", "prefill", "prefill_tcgen05"])
 def test_attention_finds_a_far_key_and_respects_the_windows_edge(K, kernel):
     """One key among hundreds is made to dominate.  Without a window the output must be its
     value; with a window ending just before it, it must not show; with one that just includes it, it must."""
-    nh, nkv, hd, n = 4, 2, 32, 333
+    nh, nkv, hd, n = 4, 2, (64 if kernel == "prefill_tcgen05" else 32), 333
     dtype = torch.float32 if kernel == "generic_f32" else torch.bfloat16
     far = 70                                                  # on the second page
     for window, visible in ((None, True), (n - far, True), (n - far - 1, False)):
@@ -290,9 +290,13 @@ def test_attention_finds_a_far_key_and_respects_the_windows_edge(K, kernel):
             got = K.attention_generic(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], pos, row, window, 1.0)
         elif kernel == "decode":
             got = K.attention_decode(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], pos, row, window, 1.0, 512)
-        else:
+        elif kernel == "prefill":
             tiles = K.prefill_tiles([1], [n - 1], "cuda")
             got = K.attention_prefill(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], tiles, 1, window, 1.0)
+        else:
+            tiles = K.prefill_tiles([1], [n - 1], "cuda", K.PREFILL_TILE_TCGEN05)
+            got = K.attention_prefill_tcgen05(qd, nh * hd, nh, nkv, hd, kp, vp, table, table.shape[1], tiles, 1, window, 1.0)
+            K.check_status("cuda")
         head3 = got.float().cpu().view(nh, hd)[3]
         hit = torch.allclose(head3, paged.v[0][far, 1], atol=3e-2)
         assert hit == visible, (kernel, window, head3[:4], paged.v[0][far, 1][:4])
