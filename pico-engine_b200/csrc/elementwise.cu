@@ -65,47 +65,118 @@ __device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float
     *reinterpret_cast<uint2*>(o) = v;
 }
 
-template <typename TO>
-__global__ void rmsnorm_kernel(const float* x, const int* rows_index,
+__device__ __forceinline__ float4 load4_as_f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_as_f(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// With ADD the row of y is first added to the row of x, which is written back: the residual sum
+// that precedes the norm, in the same pass.  A thread keeps up to RN_KEEP groups of four elements in
+// registers between the two passes and fetches their weights before the block-wide sum, so that
+// the sum's latency hides the fetch; longer rows are read again.
+#define RN_KEEP 4
+
+template <typename TO, typename TY, bool ADD>
+__global__ void rmsnorm_kernel(float* x, const TY* y, const int* rows_index,
                                const void* w, int w_dtype, float eps, TO* out, int H) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows_index ? rows_index[r] : r) * H;
+    const size_t src = rows_index ? rows_index[r] : r;
+    float* xr = x + src * H;
     TO* o = out + (size_t)r * H;
     float ss = 0.f;
     if ((H & 3) == 0) {                                       // rows start on 16-byte boundaries
-        const float4* x4 = reinterpret_cast<const float4*>(xr);
-        for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-            const float4 v = x4[i];
-            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        float4* x4 = reinterpret_cast<float4*>(xr);
+        const int n4 = H / 4;
+        float4 v[RN_KEEP], wv[RN_KEEP];
+#pragma unroll
+        for (int k = 0; k < RN_KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) {
+                v[k] = x4[i];
+                if (ADD) {
+                    const float4 a = load4_as_f(y + src * H + 4 * i);
+                    v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w;
+                    x4[i] = v[k];
+                }
+                ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss); ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+            }
+        }
+        for (int i = threadIdx.x + RN_KEEP * blockDim.x; i < n4; i += blockDim.x) {
+            float4 u = x4[i];
+            if (ADD) {
+                const float4 a = load4_as_f(y + src * H + 4 * i);
+                u.x += a.x; u.y += a.y; u.z += a.z; u.w += a.w;
+                x4[i] = u;
+            }
+            ss = fmaf(u.x, u.x, ss); ss = fmaf(u.y, u.y, ss); ss = fmaf(u.z, u.z, ss); ss = fmaf(u.w, u.w, ss);
+        }
+#pragma unroll
+        for (int k = 0; k < RN_KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) wv[k] = make_float4(load_as_f(w, w_dtype, 4 * i), load_as_f(w, w_dtype, 4 * i + 1),
+                                            load_as_f(w, w_dtype, 4 * i + 2), load_as_f(w, w_dtype, 4 * i + 3));
         }
         ss = block_sum(ss, scratch);
         const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
-        for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-            const float4 v = x4[i];
-            store4(o + 4 * i, v.x * rstd * load_as_f(w, w_dtype, 4 * i), v.y * rstd * load_as_f(w, w_dtype, 4 * i + 1),
-                   v.z * rstd * load_as_f(w, w_dtype, 4 * i + 2), v.w * rstd * load_as_f(w, w_dtype, 4 * i + 3));
+#pragma unroll
+        for (int k = 0; k < RN_KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) store4(o + 4 * i, v[k].x * rstd * wv[k].x, v[k].y * rstd * wv[k].y, v[k].z * rstd * wv[k].z, v[k].w * rstd * wv[k].w);
+        }
+        for (int i = threadIdx.x + RN_KEEP * blockDim.x; i < n4; i += blockDim.x) {
+            const float4 u = x4[i];                           // this thread wrote it, if anyone did
+            store4(o + 4 * i, u.x * rstd * load_as_f(w, w_dtype, 4 * i), u.y * rstd * load_as_f(w, w_dtype, 4 * i + 1),
+                   u.z * rstd * load_as_f(w, w_dtype, 4 * i + 2), u.w * rstd * load_as_f(w, w_dtype, 4 * i + 3));
         }
         return;
     }
-    for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float u = xr[i];
+        if (ADD) { u += to_f(y[src * H + i]); xr[i] = u; }
+        ss = fmaf(u, u, ss);
+    }
     ss = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(xr[i] * rstd * load_as_f(w, w_dtype, i));
 }
 
-extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, int w_dtype, float eps, void* out,
-                          int out_dtype, int rows, int H, void* stream) {
-    if (rows <= 0) return 0;
-    cudaStream_t s = (cudaStream_t)stream;
+template <typename TY, bool ADD>
+static int rmsnorm_launch(float* x, const TY* y, const int* rows_index, const void* w, int w_dtype, float eps, void* out,
+                          int out_dtype, int rows, int H, cudaStream_t s) {
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
-    if (out_dtype == PE_F32) PE_TRY(pe_launch(rmsnorm_kernel<float>, rows, threads, 0, s, x, rows_index, w, w_dtype, eps, (float*)out, H));
-    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(rmsnorm_kernel<bf16>, rows, threads, 0, s, x, rows_index, w, w_dtype, eps, (bf16*)out, H));
+    if (out_dtype == PE_F32) PE_TRY(pe_launch(rmsnorm_kernel<float, TY, ADD>, rows, threads, 0, s, x, y, rows_index, w, w_dtype, eps, (float*)out, H));
+    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(rmsnorm_kernel<bf16, TY, ADD>, rows, threads, 0, s, x, y, rows_index, w, w_dtype, eps, (bf16*)out, H));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
+}
+
+extern "C" int pe_rmsnorm(const float* x, const int* rows_index, const void* w, int w_dtype, float eps, void* out,
+                          int out_dtype, int rows, int H, void* stream) {
+    if (rows <= 0) return 0;
+    return rmsnorm_launch<float, false>(const_cast<float*>(x), (const float*)nullptr, rows_index, w, w_dtype, eps, out, out_dtype, rows, H,
+                                        (cudaStream_t)stream);
+}
+
+// x += y (every row, in place), then out = norm(x) * w: the residual sum and the norm that follows it in one pass
+extern "C" int pe_add_rmsnorm(float* x, const void* y, int y_dtype, const void* w, int w_dtype, float eps, void* out,
+                              int out_dtype, int rows, int H, void* stream) {
+    if (rows <= 0) return 0;
+    if (y_dtype == PE_BF16) {
+        if ((H & 3) == 0 && ((uintptr_t)y & 7)) return PE_ERR_UNSUPPORTED;
+        return rmsnorm_launch<bf16, true>(x, (const bf16*)y, nullptr, w, w_dtype, eps, out, out_dtype, rows, H, (cudaStream_t)stream);
+    }
+    if (y_dtype == PE_F32) {
+        if ((H & 3) == 0 && ((uintptr_t)y & 15)) return PE_ERR_UNSUPPORTED;
+        return rmsnorm_launch<float, true>(x, (const float*)y, nullptr, w, w_dtype, eps, out, out_dtype, rows, H, (cudaStream_t)stream);
+    }
+    return PE_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- SwiGLU
@@ -122,25 +193,41 @@ __global__ void swiglu_kernel(const T* gu, T* out, int I, size_t total) {
     }
 }
 
-// I a multiple of 8: eight bfloat16 per thread with 16-byte loads and stores
+// I a multiple of 8: eight bfloat16 per thread and step with 16-byte loads and stores, two steps in
+// flight.  The sigmoid uses the special-function unit's 2^x and reciprocal (relative error about
+// 2^-22, far below the bfloat16 rounding of the result); the exact routines cost several times
+// the memory time of this kernel.
+__device__ __forceinline__ float silu_mul_fast(float g, float u) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r * u;
+}
+__device__ __forceinline__ uint4 swiglu8(const uint4 g, const uint4 u) {
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
+        o2[e] = __floats2bfloat162_rn(silu_mul_fast(gf.x, uf.x), silu_mul_fast(gf.y, uf.y));
+    }
+    return o;
+}
 __global__ void swiglu_bf16x8_kernel(const bf16* gu, bf16* out, int I, size_t groups) {
     pdl_launch_dependents();
     pdl_wait();
     const int per_row = I / 8;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / per_row, i = (idx % per_row) * 8;
-        const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
-        const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
-        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-        uint4 o;
-        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
-            o2[e] = __floats2bfloat162_rn(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
-        }
-        *reinterpret_cast<uint4*>(out + t * I + i) = o;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += 2 * stride) {
+        const size_t idx1 = idx + stride;
+        const bool two = idx1 < groups;
+        const size_t t0 = idx / per_row, i0 = (idx % per_row) * 8, t1 = two ? idx1 / per_row : t0, i1 = two ? (idx1 % per_row) * 8 : i0;
+        const uint4 g0 = *reinterpret_cast<const uint4*>(gu + t0 * 2 * I + i0), u0 = *reinterpret_cast<const uint4*>(gu + t0 * 2 * I + I + i0);
+        const uint4 g1 = *reinterpret_cast<const uint4*>(gu + t1 * 2 * I + i1), u1 = *reinterpret_cast<const uint4*>(gu + t1 * 2 * I + I + i1);
+        *reinterpret_cast<uint4*>(out + t0 * I + i0) = swiglu8(g0, u0);
+        if (two) *reinterpret_cast<uint4*>(out + t1 * I + i1) = swiglu8(g1, u1);
     }
 }
 
@@ -149,8 +236,8 @@ extern "C" int pe_swiglu(const void* gu, void* out, int dtype, int T, int I, voi
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)T * I;
     if (dtype == PE_BF16 && I % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
-        const size_t groups = total / 8;
-        const int blocks = (int)((groups + 255) / 256 < 148 * 16 ? (groups + 255) / 256 : 148 * 16);
+        const size_t groups = total / 8, want = (groups + 511) / 512;      // two groups a thread
+        const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
         PE_TRY(pe_launch(swiglu_bf16x8_kernel, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, groups));
         PE_LAUNCH_CHECK();
         return 0;
@@ -171,14 +258,6 @@ __global__ void residual_add_kernel(float* x, const T* y, size_t total) {
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         x[i] += to_f(y[i]);
-}
-
-__device__ __forceinline__ float4 load4_as_f(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4_as_f(const bf16* p) {
-    const uint2 v = *reinterpret_cast<const uint2*>(p);
-    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-    return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
 // total a multiple of 4, both pointers aligned for 4-element accesses

@@ -74,6 +74,20 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += y (float32 rows [T, H], in place), then RMSNorm of every row: the residual sum and the
+    norm that follows it in one pass over the stream."""
+    T, H = x.shape
+    _need(x, "x", torch.float32); _need(y, "y", None, (T, H)); _need(weight, "weight", None, (H,))
+    if out is None:
+        out = torch.empty(T, H, dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype, (T, H))
+    check(core().pe_add_rmsnorm(x.data_ptr(), y.data_ptr(), _code(y, "y"), weight.data_ptr(), _code(weight, "weight"),
+                                float(eps), out.data_ptr(), _code(out, "out"), T, H, stream_ptr()), "add_rmsnorm")
+    return out
+
+
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(gate) * up of [T, 2I] (gate first) as [T, I]."""
     T, I2 = gate_up.shape

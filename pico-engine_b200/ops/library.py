@@ -19,6 +19,7 @@ _SIGNATURES = {
     "pe_embed": [P, I, P, P, I, I, I, P],
     "pe_select_tokens": [P, P, P, I, P],
     "pe_rmsnorm": [P, P, P, I, F, P, I, I, I, P],
+    "pe_add_rmsnorm": [P, P, I, P, I, F, P, I, I, I, P],
     "pe_swiglu": [P, P, I, I, I, P],
     "pe_residual_add": [P, P, I, LL, P],
     "pe_bias_add": [P, I, P, I, I, I, P],

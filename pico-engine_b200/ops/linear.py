@@ -14,7 +14,7 @@ kernel for a matrix product.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Callable, Optional
 
 import torch
 
@@ -29,7 +29,11 @@ TCGEN05_MIN_ROWS = 512      # below this its 128-row tiles leave most SMs withou
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
+           defer_add: Optional[Callable[[torch.Tensor], None]] = None) -> torch.Tensor:
+    """``defer_add``: where the product comes from the library and its sum into ``accumulate_into`` would be a
+    pass of its own, the product is handed to this function instead, and the caller adds it later (with the
+    norm that follows, in one pass)."""
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         M = a.shape[0]
         if kernels.fused_takes(M, w, a):
@@ -44,6 +48,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             if bias is not None:
                 kernels.bias_add(y, bias)
         if accumulate_into is not None:
+            if defer_add is not None:
+                defer_add(y)
+                return accumulate_into
             return kernels.residual_add(accumulate_into, y)
         return y if (out_dtype or a.dtype) == y.dtype else y.to(out_dtype)
     return kernels.linear_simt(a, w, bias, out_dtype, accumulate_into)

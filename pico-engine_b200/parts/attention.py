@@ -87,8 +87,11 @@ class GQAAttention(Mixer):
                 and (self.b_qkv is None or self.b_qkv.dtype in (torch.bfloat16, torch.float32))
                 and kernels.fused_takes(x.shape[0], self.w_qkv, x) and kernels.fused_takes(x.shape[0], self.w_o))
 
+    takes_pending = True
+
     def add_to(self, x, norm, ctx, entry, cache_entry, owns_cache):
         if self._fused(x, norm, ctx):
+            ctx.settle(x)
             s = self.spec
             kv = ctx.kv(cache_entry)
             cos, sin = getattr(self.position, "cos", None), getattr(self.position, "sin", None)
@@ -102,5 +105,5 @@ class GQAAttention(Mixer):
                                   ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
             kernels.linear_fused(a, self.w_o, accumulate_into=x)
             return
-        a = self._attend(norm.forward(x, ctx.dtype), ctx, cache_entry, owns_cache)
-        linear(a, self.w_o, accumulate_into=x)
+        a = self._attend(ctx.normed(x, norm), ctx, cache_entry, owns_cache)
+        linear(a, self.w_o, accumulate_into=x, defer_add=lambda y: ctx.defer_add(x, y))

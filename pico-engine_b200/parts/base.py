@@ -7,7 +7,8 @@ tensors by the names in its spec, and everything about the running step from the
 
 Interfaces
 ----------
-Norm          ``forward(x_f32 [T,H], out_dtype, rows_index=None) -> [rows,H]``
+Norm          ``forward(x_f32 [T,H], out_dtype, rows_index=None) -> [rows,H]``; optionally
+              ``add_forward(x, y, out_dtype)``: x += y and the norm in one pass
 Position      ``prepare(max_positions)``; ``rotate_and_store(qkv, n_q, n_kv, head_dim, ctx, kv)``
 Mixer         ``cache_needs()``; ``prepare(max_positions)``; ``apply(h, ctx, entry, cache_entry,
               owns_cache) -> y``; optionally ``add_to(x, norm, ctx, ...)`` fused
@@ -58,6 +59,27 @@ class StepContext:
     tables: Dict[int, torch.Tensor] = field(default_factory=dict)    # group -> int32 [B, stride]
     max_context: int = 0                  # upper bound of any row's length after the step
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)   # named buffers that live as long as the step
+    pending: Optional[torch.Tensor] = None  # a product [T, hidden] that still has to be added to the residual stream
+
+    # A part whose product comes out of the library may leave the sum into the residual stream pending, so
+    # that the norm that follows does both in one pass.  Whoever reads the stream first settles it: parts
+    # that declare ``takes_pending`` through ``normed``, everyone else through the arrangement.
+    def defer_add(self, x: torch.Tensor, y: torch.Tensor) -> None:
+        self.settle(x)
+        self.pending = y
+
+    def settle(self, x: torch.Tensor) -> None:
+        if self.pending is not None:
+            from ..ops import kernels
+            y, self.pending = self.pending, None
+            kernels.residual_add(x, y.contiguous())
+
+    def normed(self, x: torch.Tensor, norm: "Norm") -> torch.Tensor:
+        """norm(x) in the step's dtype, after what is pending has been added to x."""
+        if self.pending is None:
+            return norm.forward(x, self.dtype)
+        y, self.pending = self.pending, None
+        return norm.add_forward(x, y.contiguous(), self.dtype)
 
     def kv(self, cache_entry: int) -> KVView:
         g = self.cache.group_of[cache_entry]
@@ -92,6 +114,12 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows_index: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def add_forward(self, x: torch.Tensor, y: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """x += y in place, then forward(x); norms override this to do both in one pass."""
+        from ..ops import kernels
+        kernels.residual_add(x, y)
+        return self.forward(x, out_dtype)
+
 
 class Position(Part):
     def rotate_and_store(self, qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, ctx: StepContext,
@@ -100,6 +128,8 @@ class Position(Part):
 
 
 class Mixer(Part):
+    takes_pending = False      # True: add_to copes with a sum that is still pending (StepContext.normed / settle)
+
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds()
 
@@ -113,6 +143,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_pending = False
+
     def apply(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 

@@ -27,5 +27,9 @@ class Layer:
 @register_arrangement("pre_norm")
 def pre_norm(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
     """x += mixer(norm(x)); x += feed_forward(norm(x))  (pico-engine src/pico_engine/model.py:167-237)."""
+    if not layer.mixer.takes_pending:
+        ctx.settle(x)
     layer.mixer.add_to(x, layer.mixer_norm, ctx, entry, cache_entry, owns_cache)
+    if not layer.feed_forward.takes_pending:
+        ctx.settle(x)
     layer.feed_forward.add_to(x, layer.feed_forward_norm, ctx)

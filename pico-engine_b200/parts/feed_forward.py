@@ -36,12 +36,16 @@ class SwiGLU(FeedForward):
     def apply(self, h, ctx):
         return linear(self._activation(h, ctx), self.w_down, out_dtype=ctx.dtype)
 
+    takes_pending = True
+
     def add_to(self, x, norm, ctx):
         from .norm import RMSNorm
         if (ctx.dtype == torch.bfloat16 and type(norm) is RMSNorm and self.spec.intermediate % 8 == 0
                 and kernels.fused_takes(x.shape[0], self.w_gate_up, x) and kernels.fused_takes(x.shape[0], self.w_down)):
             # decoding a few sequences: norm, gate and up products and the activation are one kernel
+            ctx.settle(x)
             act = kernels.norm_gate_up_swiglu(x, norm.weight, norm.eps, self.w_gate_up)
             kernels.linear_fused(act, self.w_down, accumulate_into=x)
             return
-        linear(self._activation(norm.forward(x, ctx.dtype), ctx), self.w_down, accumulate_into=x)
+        linear(self._activation(ctx.normed(x, norm), ctx), self.w_down, accumulate_into=x,
+               defer_add=lambda y: ctx.defer_add(x, y))

@@ -64,6 +64,7 @@ class DecoderModel:
         for e, entry in enumerate(self.plan.schedule):
             cache_entry = e if entry.cache_of is None else entry.cache_of
             self.layers[entry.layer].run(x, ctx, e, cache_entry, entry.cache_of is None)
+        ctx.settle(x)
         return x
 
     def logits(self, x: torch.Tensor, rows_index: torch.Tensor) -> torch.Tensor:

@@ -25,3 +25,6 @@ class RMSNorm(Norm):
 
     def forward(self, x, out_dtype, rows_index=None):
         return kernels.rmsnorm(x, self.weight, self.eps, out_dtype, rows_index)
+
+    def add_forward(self, x, y, out_dtype):
+        return kernels.add_rmsnorm(x, y, self.weight, self.eps, out_dtype)

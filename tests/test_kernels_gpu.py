@@ -54,6 +54,21 @@ def test_rmsnorm(K, H, wdtype, odtype):
     assert torch.allclose(got.float().cpu(), want[rows.long()], atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("H", [100, 896, 2052, 5120])
+@pytest.mark.parametrize("ydtype", ["f32", "bf16"])
+def test_add_rmsnorm(K, H, ydtype):
+    """The residual sum and the norm in one pass: x is updated in place, the norm is of the sum.
+    2052 and 5120 columns leave a thread more groups than it keeps in registers."""
+    x, y, w = rnd(9, H, seed=1, scale=3.0), bf(rnd(9, H, seed=4)), bf(1 + rnd(H, seed=2) * 0.1)
+    xd = dev(x.clone())
+    got = K.add_rmsnorm(xd, dev(y.to(DT[ydtype])), dev(w.to(torch.bfloat16)), 1e-6, torch.bfloat16)
+    assert torch.allclose(xd.cpu(), x + y, atol=1e-6)
+    assert torch.allclose(got.float().cpu(), plain.rms_norm(x + y, w, 1e-6), atol=2e-2, rtol=2e-2)
+    # the same numbers as the two kernels one after the other
+    xs = K.residual_add(dev(x.clone()), dev(y.to(DT[ydtype])))
+    assert torch.equal(got, K.rmsnorm(xs, dev(w.to(torch.bfloat16)), 1e-6, torch.bfloat16))
+
+
 def test_rmsnorm_eps_matters(K):
     x, w = torch.full((1, 64), 1e-3), torch.ones(64)
     for eps in (1e-6, 1e-2):
@@ -62,9 +77,10 @@ def test_rmsnorm_eps_matters(K):
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_swiglu(K, dtype):
-    gu = bf(rnd(5, 2 * 352, seed=3, scale=2.0))
-    want = plain.swiglu(gu[:, :352], gu[:, 352:])
+@pytest.mark.parametrize("T,I", [(5, 352), (3, 4864), (700, 1000)])
+def test_swiglu(K, dtype, T, I):
+    gu = bf(rnd(T, 2 * I, seed=3, scale=2.0))
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
     got = K.swiglu(dev(gu.to(DT[dtype])))
     assert torch.allclose(got.float().cpu(), want, atol=1e-5 if dtype == "f32" else 3e-2, rtol=1e-5 if dtype == "f32" else 1e-2)
 
