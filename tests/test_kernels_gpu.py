@@ -69,6 +69,19 @@ def test_add_rmsnorm(K, H, ydtype):
     assert torch.equal(got, K.rmsnorm(xs, dev(w.to(torch.bfloat16)), 1e-6, torch.bfloat16))
 
 
+@pytest.mark.parametrize("H", [100, 896, 1024, 1028])
+def test_rmsnorm_of_many_rows(K, H):
+    """More rows than the device holds blocks at once."""
+    x, y, w = rnd(2601, H, seed=1, scale=3.0), bf(rnd(2601, H, seed=4)), bf(1 + rnd(H, seed=2) * 0.1)
+    for odtype, tol in (("f32", 1e-5), ("bf16", 2e-2)):
+        got = K.rmsnorm(dev(x), dev(w), 1e-6, DT[odtype])
+        assert torch.allclose(got.float().cpu(), plain.rms_norm(x, w, 1e-6), atol=tol, rtol=tol)
+    xd = dev(x.clone())
+    got = K.add_rmsnorm(xd, dev(y.to(torch.bfloat16)), dev(w.to(torch.bfloat16)), 1e-6, torch.bfloat16)
+    assert torch.allclose(xd.cpu(), x + y, atol=1e-6)
+    assert torch.allclose(got.float().cpu(), plain.rms_norm(x + y, w, 1e-6), atol=2e-2, rtol=2e-2)
+
+
 def test_rmsnorm_eps_matters(K):
     x, w = torch.full((1, 64), 1e-3), torch.ones(64)
     for eps in (1e-6, 1e-2):
