@@ -19,14 +19,17 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    # the passing case first and cheaply: these checks run a few hundred times a step
+    if (t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype)
+            and (shape is None or t.shape == shape or tuple(t.shape) == tuple(shape))):
+        return
     if not t.is_cuda:
         raise KernelError(f"{name} must live on a CUDA device")
     if not t.is_contiguous():
         raise KernelError(f"{name} must be contiguous")
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{name} must be {dtype}, not {t.dtype}")
-    if shape is not None and tuple(t.shape) != tuple(shape):
-        raise KernelError(f"{name} must have shape {tuple(shape)}, not {tuple(t.shape)}")
+    raise KernelError(f"{name} must have shape {tuple(shape)}, not {tuple(t.shape)}")
 
 
 def _code(t: torch.Tensor, name: str) -> int:
@@ -289,7 +292,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
     check(lib.pe_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
                                   n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context),
-                                  status_word(q.device).data_ptr(), stream_ptr()), "attention_decode")
+                                  status_ptr(q.device), stream_ptr()), "attention_decode")
     return out
 
 
@@ -353,7 +356,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, n_heads: int, n_kv
     check(for_head_dim(head_dim).pe_attention_prefill_tcgen05(
         q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], block_table.data_ptr(),
         table_stride, tiles.data_ptr(), tiles.shape[0], n_tokens, n_heads, n_kv_heads, head_dim, window or 0,
-        float(scale), status_word(q.device).data_ptr(), stream_ptr()), "attention_prefill_tcgen05")
+        float(scale), status_ptr(q.device), stream_ptr()), "attention_prefill_tcgen05")
     return out
 
 
@@ -385,10 +388,28 @@ def attention(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, hea
 FUSED_MAX_ROWS = 16
 
 
+_status_words = {}
+
+
 def status_word(device) -> torch.Tensor:
     """The int32 word in which a kernel records that a bounded wait of its own ran out (0: none did)."""
-    from .workspace import scratch
-    return scratch("status", 4, torch.device(device), zeroed=True)[:4].view(torch.int32)
+    word = _status_words.get(device)
+    if word is None:
+        from .workspace import scratch
+        word = _status_words[device] = scratch("status", 4, torch.device(device), zeroed=True)[:4].view(torch.int32)
+        _status_ptrs[device] = word.data_ptr()
+    return word
+
+
+_status_ptrs = {}
+
+
+def status_ptr(device) -> int:
+    """The address of ``status_word(device)``."""
+    ptr = _status_ptrs.get(device)
+    if ptr is None:
+        ptr = status_word(device).data_ptr()
+    return ptr
 
 
 def check_status(device) -> None:
@@ -439,7 +460,7 @@ def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torc
     check(core().pe_linear_fused(_ptr(a), _ptr(norm_of), _ptr(norm_weight),
                                  0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
                                  w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
-                                 epilogue, M, N, K, status_word(w.device).data_ptr(), stream_ptr()), "linear_fused")
+                                 epilogue, M, N, K, status_ptr(w.device), stream_ptr()), "linear_fused")
     return out
 
 
@@ -450,7 +471,7 @@ def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
     _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
     act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
     check(core().pe_norm_gate_up_swiglu(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
-                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_word(x.device).data_ptr(),
+                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_ptr(x.device),
                                         stream_ptr()), "norm_gate_up_swiglu")
     return act
 
@@ -481,7 +502,7 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
                                         float(eps), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
                                         q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
                                         tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
-                                        1 if store else 0, status_word(x.device).data_ptr(), stream_ptr()), "norm_qkv_rope_store")
+                                        1 if store else 0, status_ptr(x.device), stream_ptr()), "norm_qkv_rope_store")
     return q
 
 
@@ -510,6 +531,6 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     else:
         out, epilogue = torch.empty(M, N, dtype=torch.bfloat16, device=a.device), 0
     check(core().pe_gemm_tcgen05(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
-                                 out.data_ptr(), epilogue, M, N, K, status_word(a.device).data_ptr(), stream_ptr()),
+                                 out.data_ptr(), epilogue, M, N, K, status_ptr(a.device), stream_ptr()),
           "gemm_tcgen05")
     return out
