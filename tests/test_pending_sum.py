@@ -1,0 +1,119 @@
+"""The residual sum that a part may leave pending for the next norm (CPU): who settles it, and when.
+
+The kernels are replaced by torch arithmetic; what is tested is the bookkeeping of
+``StepContext.defer_add / settle / normed`` and of the ``pre_norm`` arrangement.
+"""
+import torch
+
+import pico_engine.ops.kernels as kernels
+from pico_engine.parts import base
+from pico_engine.parts.block import pre_norm
+
+
+def context():
+    z = torch.zeros(0, dtype=torch.int32)
+    return base.StepContext(T=3, B=1, dtype=torch.float32, device=torch.device("cpu"), tok_pos=z, tok_row=z, slots=z,
+                            slot_ids=[0], lens=[3], starts=[0], one_token_each=False, cache=None)
+
+
+class CountingNorm(base.Norm):
+    """Doubles its input; counts which of its two entry points ran."""
+
+    def __init__(self):
+        self.plain = self.fused = 0
+
+    def forward(self, x, out_dtype, rows_index=None):
+        self.plain += 1
+        return 2 * x
+
+    def add_forward(self, x, y, out_dtype):
+        self.fused += 1
+        x += y
+        return 2 * x
+
+
+class Knowing(base.FeedForward):
+    """A part that copes with a pending sum and leaves its own pending."""
+    takes_pending = True
+
+    def __init__(self):
+        pass
+
+    def add_to(self, x, norm, ctx):
+        h = ctx.normed(x, norm)
+        ctx.defer_add(x, h + 1)
+
+
+class Plain(base.Mixer):
+    """A part that knows nothing of pending sums: it reads x directly."""
+
+    def __init__(self):
+        self.saw = None
+
+    def add_to(self, x, norm, ctx, entry, cache_entry, owns_cache):
+        self.saw = x.clone()
+        x += 10
+
+
+class Layer:
+    def __init__(self, mixer, feed_forward):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = CountingNorm(), CountingNorm()
+
+
+def test_pending_sum_is_added_by_the_next_norm_or_settled_before_a_part_that_reads_x(monkeypatch):
+    adds = []
+
+    def residual_add(x, y):
+        adds.append(1)
+        x += y
+        return x
+
+    monkeypatch.setattr(kernels, "residual_add", residual_add)
+    ctx, x = context(), torch.ones(3, 4)
+
+    # a knowing part: norm(1) = 2, pending 3
+    ff = Knowing()
+    norm = CountingNorm()
+    ff.add_to(x, norm, ctx)
+    assert ctx.pending is not None and torch.equal(x, torch.ones(3, 4)) and (norm.plain, norm.fused) == (1, 0)
+    # the next knowing part's norm adds it in the same pass: x = 4, norm = 8, pending 9
+    ff.add_to(x, norm, ctx)
+    assert torch.equal(x, torch.full((3, 4), 4.0)) and (norm.plain, norm.fused) == (1, 1) and not adds
+    assert torch.equal(ctx.pending, torch.full((3, 4), 9.0))
+
+    # a layer whose mixer reads x itself: the arrangement settles first (x = 13), the mixer sees the settled stream
+    layer = Layer(Plain(), Knowing())
+    pre_norm(layer, x, ctx, 0, 0, True)
+    assert len(adds) == 1 and torch.equal(layer.mixer.saw, torch.full((3, 4), 13.0))
+    # mixer: x = 23; feed-forward: norm 46, pending 47
+    assert torch.equal(x, torch.full((3, 4), 23.0)) and torch.equal(ctx.pending, torch.full((3, 4), 47.0))
+    assert (layer.feed_forward_norm.plain, layer.feed_forward_norm.fused) == (1, 0)
+
+    # the end of the layers: what is pending is added, once
+    ctx.settle(x)
+    ctx.settle(x)
+    assert len(adds) == 2 and ctx.pending is None and torch.equal(x, torch.full((3, 4), 70.0))
+
+
+def test_a_second_deferred_sum_settles_the_first(monkeypatch):
+    monkeypatch.setattr(kernels, "residual_add", lambda x, y: x.add_(y))
+    ctx, x = context(), torch.zeros(2, 2)
+    ctx.defer_add(x, torch.ones(2, 2))
+    ctx.defer_add(x, torch.full((2, 2), 5.0))
+    assert torch.equal(x, torch.ones(2, 2)) and torch.equal(ctx.pending, torch.full((2, 2), 5.0))
+
+
+def test_the_default_norm_adds_then_norms(monkeypatch):
+    monkeypatch.setattr(kernels, "residual_add", lambda x, y: x.add_(y))
+
+    class OnlyForward(base.Norm):
+        def __init__(self):
+            pass
+
+        def forward(self, x, out_dtype, rows_index=None):
+            return x * 3
+
+    x = torch.ones(2, 2)
+    h = OnlyForward().add_forward(x, torch.ones(2, 2), torch.float32)
+    assert torch.equal(x, torch.full((2, 2), 2.0)) and torch.equal(h, torch.full((2, 2), 6.0))
