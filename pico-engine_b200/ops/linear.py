@@ -41,6 +41,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         if (accumulate_into is not None and bias is None and w.numel() <= TCGEN05_MAX_WEIGHT and TCGEN05_MIN_ROWS <= M <= TCGEN05_MAX_ROWS
                 and kernels.gemm_tcgen05_takes(a, w)):
             return kernels.gemm_tcgen05(a, w, accumulate_into=accumulate_into)
+        if bias is None and accumulate_into is None and out_dtype == torch.float32:
+            return torch.mm(a, w.t(), out_dtype=torch.float32)   # the logits: the library's float32 accumulator as it is
         if bias is not None and bias.dtype == a.dtype:
             y = torch.addmm(bias, a, w.t())                  # the library adds the bias in its epilogue
         else:
