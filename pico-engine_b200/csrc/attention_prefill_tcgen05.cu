@@ -448,7 +448,7 @@ int at_make_map(CUtensorMap* map, const void* base, long long rows, long long co
 
 extern "C" int pe_attention_prefill_tcgen05_tile() { return AT_QTILE; }
 
-// how many of the kernel's CTAs an SM holds at once (2 at head size 64, 1 at 128), or a negative CUDA error
+// how many of the kernel's CTAs an SM holds at once (one: it takes all of tensor memory), or a negative CUDA error
 extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() {
     int n = 0;
     if (cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM_BYTES) != cudaSuccess) return -1;
