@@ -43,7 +43,16 @@ TINY_B = {
     "max_position_embeddings": 256, "tie_word_embeddings": False, "use_sliding_window": True,
     "sliding_window": 32, "max_window_layers": 1, "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
-TINY = {"A": TINY_A, "B": TINY_B}
+# A third one at head size 64, where prompts take the tcgen05 attention kernel: a window on the upper layer that is
+# no multiple of a page, a vocabulary and widths that are no powers of two.
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 64,
+    "intermediate_size": 200, "vocab_size": 328, "rope_theta": 50000.0, "rms_norm_eps": 3e-6,
+    "max_position_embeddings": 512, "tie_word_embeddings": False, "use_sliding_window": True,
+    "sliding_window": 70, "max_window_layers": 1, "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 
 
 def tensor_shapes(cfg: dict) -> dict:

@@ -12,7 +12,7 @@ from conftest import TINY, close_enough, make_weights, write_model
 
 pytestmark = pytest.mark.gpu
 
-SEEDS = {"A": 0, "B": 1}
+SEEDS = {"A": 0, "B": 1, "C": 2}
 
 
 def random_requests(cfg, lengths, seed):
@@ -34,8 +34,9 @@ def models(tmp_path_factory):
     return out
 
 
-LENGTHS = {"A": [5, 9, 13, 40, 66, 100, 33, 1], "B": [1, 17, 40, 64, 65, 130, 200, 35]}
-CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")]
+LENGTHS = {"A": [5, 9, 13, 40, 66, 100, 33, 1], "B": [1, 17, 40, 64, 65, 130, 200, 35],
+           "C": [129, 3, 300, 128, 71, 257, 64, 190]}
+CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
