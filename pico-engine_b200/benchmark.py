@@ -14,7 +14,7 @@ from __future__ import annotations
 import argparse
 import json
 import time
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Sequence
 
 import torch
 

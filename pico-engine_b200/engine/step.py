@@ -16,7 +16,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import Cache, PAGE, pages_for
+from ..cache import Cache, pages_for
 from ..parts.base import StepContext
 
 

@@ -1,6 +1,5 @@
 """The engine against the plain implementation: every way of cutting the same requests into
 steps, in float32 and in bfloat16, on both tiny configurations."""
-import os
 
 import numpy as np
 import pytest

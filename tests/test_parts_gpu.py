@@ -151,7 +151,6 @@ def plain_scheduled(cfg, w, ids, schedule):
 
 def test_the_order_of_layers_is_data():
     """Layer 0 runs twice (two caches of its own) and the last execution reads the cache of the second."""
-    import replay
     from pico_engine.cache import Cache
     from pico_engine.config import ScheduleEntry, config_from_dict
     from pico_engine.engine.step import Stepper

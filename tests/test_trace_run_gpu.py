@@ -1,10 +1,8 @@
 """bin/trace_run as a user runs it: a model folder, steps on standard input, logits on disk."""
-import json
 import os
 import subprocess
 import sys
 
-import numpy as np
 import pytest
 import torch
 

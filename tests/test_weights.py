@@ -1,6 +1,5 @@
 """The safetensors container, the checked loader and the random-weights mode (CPU)."""
 import json
-import os
 
 import pytest
 import torch
