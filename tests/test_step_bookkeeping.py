@@ -1,7 +1,8 @@
-"""The residual sum that a part may leave pending for the next norm (CPU): who settles it, and when.
+"""Host-side bookkeeping of a step (CPU): the residual sum that a part may leave pending for the next norm
+(who settles it, and when), and how a step's tokens are cut into runs for the prefill attention kernels.
 
 The kernels are replaced by torch arithmetic; what is tested is the bookkeeping of
-``StepContext.defer_add / settle / normed`` and of the ``pre_norm`` arrangement.
+``StepContext.defer_add / settle / normed``, of the ``pre_norm`` arrangement and of ``prefill_tiles``.
 """
 import torch
 
@@ -117,3 +118,20 @@ def test_the_default_norm_adds_then_norms(monkeypatch):
     x = torch.ones(2, 2)
     h = OnlyForward().add_forward(x, torch.ones(2, 2), torch.float32)
     assert torch.equal(x, torch.full((2, 2), 2.0)) and torch.equal(h, torch.full((2, 2), 6.0))
+
+
+def test_prefill_tiles_cut_runs_per_sequence_and_put_the_longest_first():
+    """The host side of the prefill attention kernels: runs of at most `tile` tokens of one sequence,
+    every packed token in exactly one run, the runs that see the most keys first."""
+    lens, starts = [130, 1, 64, 300], [0, 500, 37, 10]
+    for tile in (kernels.PREFILL_TILE, kernels.PREFILL_TILE_TCGEN05):
+        rows = kernels.prefill_tiles(lens, starts, "cpu", tile).tolist()
+        seen = []
+        first = [sum(lens[:b]) for b in range(len(lens))]
+        for b, tok0, n, pos0 in rows:
+            assert 1 <= n <= tile and pos0 - starts[b] == tok0 - first[b] and 0 <= tok0 - first[b] < lens[b]
+            assert (tok0 - first[b]) % tile == 0 and tok0 - first[b] + n <= lens[b]
+            seen.extend(range(tok0, tok0 + n))
+        assert sorted(seen) == list(range(sum(lens)))
+        ends = [pos0 + n for _, _, n, pos0 in rows]
+        assert ends == sorted(ends, reverse=True)
