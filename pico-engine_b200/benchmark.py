@@ -65,8 +65,9 @@ def prefill_flops(engine, tokens: int) -> float:
     for entry in model.plan.schedule:
         layer = model.layers[entry.layer]
         for part in (layer.mixer, layer.feed_forward):
-            flops += sum(2.0 * tokens * t.numel() for t in part.weights() if t.dim() == 2)
-        spec = layer.mixer.spec
+            if part is not None:
+                flops += sum(2.0 * tokens * t.numel() for t in part.weights() if t.dim() == 2)
+        spec = layer.mixer.spec if layer.mixer is not None else None
         if hasattr(spec, "n_heads"):
             w = spec.window
             seen = sum(min(p + 1, w) if w else p + 1 for p in range(tokens))

@@ -12,6 +12,10 @@ sequence.
   window that a later token can have, so in steady state it holds about ``window`` positions
   per sequence.
 * State: ``state [entry with state, slot, elems]`` float32, zeroed when a slot is taken.
+* Beside what sequences hold there is one *idle* slot with one page in every group (``idle_slot``,
+  ``idle_page``: the index after the last real one): a step that is padded to a fixed number of rows
+  (a captured decode step of a bucket of rows) lets its idle rows read and write there, so that
+  kernels need no notion of a row that is not there.  It takes no page and no slot from the sequences.
 
 pico-engine allocates a fresh zeroed (kv head, capacity, head_dim) pair per layer for every
 request (src/pico_engine/engine.py:119-121, 316) and keeps its recurrent model's per-layer
@@ -45,7 +49,7 @@ class KVGroup:
     table: Dict[int, List[int]]           # slot -> physical page of each logical page (-1: given back)
 
     def bytes(self) -> int:
-        return 0 if self.k is None else 2 * self.k.numel() * self.k.element_size()
+        return 0 if self.k is None else 2 * self.k.numel() * self.k.element_size()      # with the idle page
 
 
 class Cache:
@@ -78,13 +82,14 @@ class Cache:
             self.groups[g].entries.append(e)
         self.state_entries = [e for e, n in enumerate(needs) if n is not None and n.state_elems > 0]
         self.state: Dict[int, torch.Tensor] = {}
+        self.idle_slot, self.idle_page = max_seqs, self.n_pages       # one past the slots and pages that sequences use
         if allocate:
             for g in self.groups:
-                shape = (len(g.entries), self.n_pages, g.need.n_kv_heads, PAGE, g.need.head_dim)
+                shape = (len(g.entries), self.n_pages + 1, g.need.n_kv_heads, PAGE, g.need.head_dim)
                 g.k = torch.zeros(shape, dtype=dtype, device=self.device)
                 g.v = torch.zeros(shape, dtype=dtype, device=self.device)
             for e in self.state_entries:
-                self.state[e] = torch.zeros(max_seqs, needs[e].state_elems, dtype=torch.float32, device=self.device)
+                self.state[e] = torch.zeros(max_seqs + 1, needs[e].state_elems, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -107,7 +112,15 @@ class Cache:
         self.slots.give([slot])
 
     def length(self, slot: int) -> int:
-        return self.lengths[slot]
+        return 0 if slot == self.idle_slot else self.lengths[slot]
+
+    def snapshot_state(self) -> Dict[int, torch.Tensor]:
+        """A copy of the per-sequence state of every entry that has some (for running a step on trial)."""
+        return {e: t.clone() for e, t in self.state.items()}
+
+    def restore_state(self, snapshot: Dict[int, torch.Tensor]) -> None:
+        for e, t in snapshot.items():
+            self.state[e].copy_(t)
 
     def held_tokens(self) -> int:
         """Tokens held by live sequences, each rounded up to PAGE."""
@@ -142,9 +155,12 @@ class Cache:
     def page_table(self, group: int, slots: Sequence[int], width: Optional[int] = None) -> np.ndarray:
         """int32 [len(slots), width]: physical page of each logical page, -1 where there is none."""
         g = self.groups[group]
-        width = width or max(1, max(len(g.table[s]) for s in slots))
+        width = width or max(1, max(len(g.table[s]) for s in slots if s != self.idle_slot) if any(s != self.idle_slot for s in slots) else 1)
         out = np.full((len(slots), width), -1, dtype=np.int32)
         for r, s in enumerate(slots):
+            if s == self.idle_slot:
+                out[r, 0] = self.idle_page
+                continue
             row = g.table[s]
             if len(row) > width:
                 raise CacheFull(f"sequence slot {s} holds {len(row)} pages, the table has room for {width}")

@@ -94,11 +94,14 @@ class LayerSpec:
 
     ``arrangement`` names an entry of ``parts.registry.ARRANGEMENTS``; "pre_norm" is
     x += mixer(norm(x)); x += ffn(norm(x))  (pico-engine src/pico_engine/model.py:167-237).
+    Every part is optional: a block without a feed-forward is a mixer-only block (pico-engine's
+    recurrent layers are such, src/pico_engine/model.py:389-406), one without a mixer a feed-forward-only
+    block, and a half without a norm takes the residual stream as it is.
     """
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: Optional[PartSpec]
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
     arrangement: str = "pre_norm"
 
 

@@ -222,9 +222,19 @@ __device__ __forceinline__ unsigned long long ss_scan(unsigned long long v, unsi
     return before + inc - v;
 }
 
-__global__ void __launch_bounds__(SS_THREADS) sample_max_kernel(const float* logits, int V, float temperature, SsRow* rows) {
+// The sampler's settings as a kernel reads them.  A launch gives them by value; where it also gives `device`
+// (four 32-bit words and a 64-bit seed, written by the host before the launch), those are read instead, so
+// that a captured launch follows settings that change from call to call.
+struct SsSettings { float temperature; int top_k; float top_p; int unused; unsigned long long seed; };
+__device__ __forceinline__ SsSettings ss_settings(const SsSettings& by_value, const SsSettings* device) {
+    return device ? *device : by_value;
+}
+
+__global__ void __launch_bounds__(SS_THREADS) sample_max_kernel(const float* logits, int V, const SsSettings given,
+                                                                const SsSettings* device, SsRow* rows) {
     pdl_launch_dependents();
     pdl_wait();
+    const float temperature = ss_settings(given, device).temperature;
     __shared__ float fscratch[33];
     const int b = blockIdx.y;
     const float* row = logits + (size_t)b * V;
@@ -236,12 +246,14 @@ __global__ void __launch_bounds__(SS_THREADS) sample_max_kernel(const float* log
 }
 
 // One level of a selection.  by_mass 0: top-k (the k-th largest key); 1: top-p.
-__global__ void __launch_bounds__(SS_THREADS) sample_select_kernel(const float* logits, int V, float temperature,
-                                                                   SsRow* rows, unsigned int* h_count,
-                                                                   unsigned long long* h_mass, int by_mass, int level,
-                                                                   int top_k, float top_p) {
+__global__ void __launch_bounds__(SS_THREADS) sample_select_kernel(const float* logits, int V, const SsSettings given,
+                                                                   const SsSettings* device, SsRow* rows, unsigned int* h_count,
+                                                                   unsigned long long* h_mass, int by_mass, int level) {
     pdl_launch_dependents();
     pdl_wait();
+    const SsSettings set = ss_settings(given, device);
+    const float temperature = set.temperature, top_p = set.top_p;
+    const int top_k = set.top_k;
     // per bin: count, and the mass as the sums of its low 20 and its high 19 bits (native 32-bit atomics;
     // 4096 terms of a chunk cannot overflow either)
     __shared__ unsigned int s_count[SS_BINS], s_lo[SS_BINS], s_hi[SS_BINS];
@@ -350,12 +362,15 @@ __global__ void __launch_bounds__(SS_THREADS) sample_select_kernel(const float* 
     for (int i = tid; i < SS_BINS; i += SS_THREADS) { gc[i] = 0u; gm[i] = 0ull; }      // the histogram is clear again
 }
 
-__global__ void __launch_bounds__(SS_THREADS) sample_draw_kernel(const float* logits, int* out, int V, float temperature,
-                                                                 SsRow* rows, unsigned long long* chunk_mass,
-                                                                 int* chunk_last, unsigned long long seed,
+__global__ void __launch_bounds__(SS_THREADS) sample_draw_kernel(const float* logits, int* out, int V, const SsSettings given,
+                                                                 const SsSettings* device, SsRow* rows,
+                                                                 unsigned long long* chunk_mass, int* chunk_last,
                                                                  const int* request, const int* step) {
     pdl_launch_dependents();
     pdl_wait();
+    const SsSettings set = ss_settings(given, device);
+    const float temperature = set.temperature;
+    const unsigned long long seed = set.seed;
     __shared__ unsigned long long seg[SS_THREADS];
     __shared__ unsigned long long s_total, s_before;
     __shared__ int s_chunk, s_found, s_last;
@@ -450,10 +465,17 @@ extern "C" long long pe_sample_scratch_bytes(int B, int V) {
 }
 
 // `scratch`: pe_sample_scratch_bytes(B, V) bytes that are zero before the first call (every call leaves them zero).
+// `settings`: null, or 24 bytes on the device (temperature as float, top_k as int, top_p as float, a word that is
+// not read, the seed as 64 bits) that the kernels read instead of the scalar arguments; the scalar top_k and top_p
+// still say which passes are launched (whether there is a cut by rank and one by mass), so they must agree on that.
 extern "C" int pe_sample(const float* logits, int* out, int B, int V, float temperature, int top_k, float top_p,
-                         unsigned long long seed, const int* request, const int* step, void* scratch, void* stream) {
+                         unsigned long long seed, const int* request, const int* step, void* scratch, const void* settings,
+                         void* stream) {
     if (B <= 0) return 0;
-    if (V <= 0 || !(temperature > 0.f) || B > 65535 || !scratch || (((uintptr_t)scratch) & 15)) return PE_ERR_UNSUPPORTED;
+    if (V <= 0 || !(temperature > 0.f) || B > 65535 || !scratch || (((uintptr_t)scratch) & 15) || (((uintptr_t)settings) & 7))
+        return PE_ERR_UNSUPPORTED;
+    SsSettings given = {temperature, top_k, top_p, 0, seed};
+    const SsSettings* device = (const SsSettings*)settings;
     const int chunks = (V + SS_CHUNK - 1) / SS_CHUNK;
     SsRow* rows = (SsRow*)scratch;
     unsigned long long* h_mass = (unsigned long long*)(rows + B);
@@ -462,19 +484,19 @@ extern "C" int pe_sample(const float* logits, int* out, int B, int V, float temp
     int* chunk_last = (int*)(h_count + (size_t)B * SS_BINS);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(chunks, B);
-    PE_TRY(pe_launch(sample_max_kernel, grid, SS_THREADS, 0, s, logits, V, temperature, rows));
+    PE_TRY(pe_launch(sample_max_kernel, grid, SS_THREADS, 0, s, logits, V, given, device, rows));
     PE_LAUNCH_CHECK();
     const bool cut_k = top_k > 0 && top_k < V, cut_p = top_p < 1.0f;
     for (int by_mass = 0; by_mass < 2; ++by_mass) {
         if (by_mass ? !cut_p : !cut_k) continue;
         for (int level = 0; level < 3; ++level) {
-            PE_TRY(pe_launch(sample_select_kernel, grid, SS_THREADS, 0, s, logits, V, temperature, rows, h_count, h_mass,
-                             by_mass, level, top_k, top_p));
+            PE_TRY(pe_launch(sample_select_kernel, grid, SS_THREADS, 0, s, logits, V, given, device, rows, h_count, h_mass,
+                             by_mass, level));
             PE_LAUNCH_CHECK();
         }
     }
-    PE_TRY(pe_launch(sample_draw_kernel, grid, SS_THREADS, 0, s, logits, out, V, temperature, rows, chunk_mass, chunk_last,
-                     seed, request, step));
+    PE_TRY(pe_launch(sample_draw_kernel, grid, SS_THREADS, 0, s, logits, out, V, given, device, rows, chunk_mass, chunk_last,
+                     request, step));
     PE_LAUNCH_CHECK();
     return 0;
 }

@@ -20,7 +20,7 @@ from ..ops.library import core, require_cuda
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_folder, load_into, random_tensor
 from .generate import Request, generate as run_generation, held_tokens
-from .graph import GraphedDecode, TokenLoop
+from .graph import GraphedDecode, TokenLoop, bucket_rows
 from .step import Stepper
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -89,6 +89,10 @@ class Engine:
             return
         if c is not None and c.lengths:
             raise RuntimeError("the cache cannot grow while sequences are open")
+        if c is not None:                                   # it only ever grows: what it held it keeps holding
+            max_tokens = max(max_tokens, c.n_pages * PAGE)
+            max_context = max(max_context, self.stepper.max_context)
+            max_seqs = max(max_seqs, c.max_seqs)
         self.cache = self.stepper = None
         self._graphs.clear()
         self.cache = Cache(self.model.cache_needs(), max_tokens, max_seqs, self.dtype, self.device)
@@ -151,13 +155,21 @@ class EngineBackend:
         self.e.last_timing["prefill_s"] += time.perf_counter() - t0
         return chosen
 
-    def _graph(self, B: int) -> GraphedDecode:
-        key = (B, self.sampler.params)
-        g = self.e._graphs.get(key)
+    MAX_GRAPHS = 24      # captured decode steps an engine keeps (each holds its buffers); the least recently used goes
+
+    def _graph(self, rows: int) -> GraphedDecode:
+        """The captured step for ``rows`` rows: one per bucket of rows and kind of sampling.  Temperature,
+        top-k, top-p and seed are numbers the graph reads at run time, so calls that vary them share it."""
+        key = (bucket_rows(rows), self.sampler.kind(self.e.model.plan.vocab_size))
+        graphs = self.e._graphs
+        g = graphs.pop(key, None)
         if g is None:
             if self.e._token_loop is None:
                 self.e._token_loop = TokenLoop(self.e.device)
-            g = self.e._graphs[key] = GraphedDecode(self.e.stepper, self.sampler, B, self.e._token_loop)
+            g = GraphedDecode(self.e.stepper, self.sampler, key[0], self.e._token_loop)
+            while len(graphs) >= self.MAX_GRAPHS:
+                graphs.pop(next(iter(graphs)))
+        graphs[key] = g                                  # most recently used last
         return g
 
     def decode(self, slots, tokens, requests, steps) -> List[int]:
@@ -165,7 +177,7 @@ class EngineBackend:
         step's description is copied from pinned memory, the result is read back."""
         t0, sent = time.perf_counter(), self.e.stepper.h2d_bytes
         if self.use_graph:
-            chosen = self._graph(len(slots)).launch(slots, tokens, requests, steps).tokens()
+            chosen = self._graph(len(slots)).launch(slots, tokens, requests, steps, sampler=self.sampler).tokens()
         else:
             logits = self.e.stepper.step(slots, [[t] for t in tokens])
             chosen = self.sampler.choose(logits, self._int32(requests), self._int32(steps)).tolist()
@@ -188,7 +200,7 @@ class EngineBackend:
         if self._mark is None:
             self._mark = now
         flight = self._graph(len(slots)).launch(slots, [0 if s >= 0 else t for t, s in zip(tokens, sources)],
-                                                requests, steps, sources)
+                                                requests, steps, sources, sampler=self.sampler)
         t = self.e.last_timing
         t["decode_steps"] += 1
         t["h2d_bytes"] += self.e.stepper.h2d_bytes - sent

@@ -1,8 +1,12 @@
 """One decode step (every row brings one token) captured as a CUDA graph, for a fixed number of
 rows.  All that changes from step to step lives in one int32 device buffer that the host
-refreshes before each replay: token ids, positions, page tables, and the sampling counters.
-A step may also take its token ids from what the step before it chose, on the device, so that
-the host can launch it before it has read those tokens (``TokenLoop``).
+refreshes before each replay: token ids, positions, page tables, the sampling counters and the
+sampler's settings (temperature, top-k, top-p, seed).  A graph is captured for a *bucket* of rows
+(1, 2, 4, 8, ...): a step of fewer rows fills the bucket with idle rows, which bring token 0 at
+position 0 of the cache's idle slot and whose results nobody reads, so that a batch whose requests
+end one by one needs a handful of graphs, not one per row count.  A step may also take its token
+ids from what the step before it chose, on the device, so that the host can launch it before it
+has read those tokens (``TokenLoop``).
 
 pico-engine captures its one-token forward the same way (src/pico_engine/engine.py:269-306):
 static token and position buffers, three warm-up runs on a side stream, replay per token,
@@ -55,7 +59,20 @@ class TokenLoop:
         return InFlight(B, self._pinned[i], self._events[i])
 
 
+def bucket_rows(rows: int) -> int:
+    """The number of rows of the graph that runs a decode step of ``rows`` rows: the next power of two."""
+    b = 1
+    while b < rows:
+        b *= 2
+    return b
+
+
 class GraphedDecode:
+    """``B`` is the number of rows of the captured step; a launch may bring fewer.  ``sampler`` says how tokens
+    are chosen (greedy, or which cuts a draw makes: that fixes the kernels of the graph); its temperature,
+    top-k, top-p and seed are read from the device buffer at run time, so one graph serves every setting
+    of the same kind (``launch(..., sampler=)``)."""
+
     def __init__(self, stepper: Stepper, sampler, B: int, loop: Optional[TokenLoop] = None):
         self.stepper, self.sampler, self.B = stepper, sampler, B
         cache = stepper.cache
@@ -65,9 +82,10 @@ class GraphedDecode:
         self.widths = [pages_for(stepper.max_context)] * len(cache.groups)
         self.layout = StepLayout(B, B, B, self.widths)
         n = self.layout.total
-        self.extra = n                                   # request ids [B], step counters [B], token sources [B]
+        self.extra = n                                   # request ids [B], step counters [B], token sources [B], settings [6]
         self.pad = (B + 3) & ~3
-        self.dev = torch.zeros(n + 3 * self.pad, dtype=torch.int32, device=stepper.device)
+        self.settings_at = n + 3 * self.pad              # a multiple of 4 words: the 64-bit seed is aligned
+        self.dev = torch.zeros(self.settings_at + 8, dtype=torch.int32, device=stepper.device)
         self.host = np.zeros(self.dev.numel(), dtype=np.int32)
         self.tokens_out = self.loop.chosen[:B]
         self.logits: Optional[torch.Tensor] = None
@@ -77,14 +95,27 @@ class GraphedDecode:
 
     # ------------------------------------------------------------------ host side of a step
     def _fill(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int],
-              sources: Optional[Sequence[int]]) -> None:
-        lay, B, pad = self.layout, self.B, self.pad
-        _, fresh, starts = self.stepper.describe(slots, [1] * B, None, [[t] for t in tokens], self.widths)
+              sources: Optional[Sequence[int]], sampler) -> None:
+        lay, B, pad, n = self.layout, self.B, self.pad, len(slots)
+        if n > B:
+            raise ValueError(f"a step of {n} rows does not fit a graph of {B}")
+        idle = [self.stepper.cache.idle_slot] * (B - n)
+        _, fresh, starts = self.stepper.describe(list(slots) + idle, [1] * B, None, [[t] for t in tokens] + [[0]] * (B - n),
+                                                 self.widths)
         self.host[:lay.total] = fresh
-        self.host[self.extra: self.extra + B] = np.asarray(requests, dtype=np.int32)
-        self.host[self.extra + pad: self.extra + pad + B] = np.asarray(steps, dtype=np.int32)
-        self.host[self.extra + 2 * pad: self.extra + 2 * pad + B] = -1 if sources is None else np.asarray(sources, dtype=np.int32)
-        self._starts, self._slots = starts, list(slots)
+        self.host[self.extra: self.extra + B] = 0
+        self.host[self.extra: self.extra + n] = np.asarray(requests, dtype=np.int32)
+        self.host[self.extra + pad: self.extra + pad + B] = 0
+        self.host[self.extra + pad: self.extra + pad + n] = np.asarray(steps, dtype=np.int32)
+        self.host[self.extra + 2 * pad: self.extra + 2 * pad + B] = -1
+        if sources is not None:
+            self.host[self.extra + 2 * pad: self.extra + 2 * pad + n] = np.asarray(sources, dtype=np.int32)
+        p = (sampler or self.sampler).params
+        if (sampler or self.sampler).kind(self.stepper.vocab) != self.sampler.kind(self.stepper.vocab):
+            raise ValueError("this graph was captured for another kind of sampling")
+        self.host[self.settings_at: self.settings_at + 6] = kernels.sample_settings_words(
+            p.temperature if p.temperature > 0 else 1.0, p.top_k, p.top_p, p.seed)
+        self._starts, self._slots = starts, list(slots) + idle
 
     def _forward(self) -> None:
         lay, B, pad = self.layout, self.B, self.pad
@@ -96,18 +127,23 @@ class GraphedDecode:
         kernels.select_tokens(ids, self.loop.chosen, self.dev[self.extra + 2 * pad: self.extra + 2 * pad + B])
         self.logits = self.stepper.model.forward(ids, ctx, self.dev[lay.want: lay.want + B])
         self.sampler.choose(self.logits, self.dev[self.extra: self.extra + B],
-                            self.dev[self.extra + pad: self.extra + pad + B], self.tokens_out)
+                            self.dev[self.extra + pad: self.extra + pad + B], self.tokens_out,
+                            settings=self.dev[self.settings_at: self.settings_at + 6])
 
     def _capture(self) -> None:
         # The warm-up runs and the capture write the shared token buffer; what the step before chose
-        # is kept aside meanwhile, since this step may take its ids from there.
+        # is kept aside meanwhile, since this step may take its ids from there.  Keys and values are
+        # rewritten with the same numbers by every run, but per-sequence state (a mixer's running sums) would
+        # be advanced once per run: it is put back after the warm-up, so that only the replay counts.
         keep = self.loop.chosen.clone()
+        state = self.stepper.cache.snapshot_state()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(3):                           # the step is idempotent: it rewrites the same cache rows
+            for _ in range(3):
                 self.loop.chosen.copy_(keep)
                 self._forward()
+            self.stepper.cache.restore_state(state)
         torch.cuda.current_stream().wait_stream(side)
         self.loop.chosen.copy_(keep)
         graph = torch.cuda.CUDAGraph()
@@ -119,11 +155,12 @@ class GraphedDecode:
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
     def launch(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int],
-               sources: Optional[Sequence[int]] = None) -> InFlight:
-        """Start one decode step of ``B`` rows and the copy of its chosen tokens to the host.  Row j's
-        token is ``tokens[j]``, or, where ``sources[j] >= 0``, what row ``sources[j]`` of the step
-        launched before this one chose (``tokens[j]`` is then any valid id)."""
-        self._fill(slots, tokens, requests, steps, sources)
+               sources: Optional[Sequence[int]] = None, sampler=None) -> InFlight:
+        """Start one decode step of ``len(slots) <= B`` rows and the copy of its chosen tokens to the host.
+        Row j's token is ``tokens[j]``, or, where ``sources[j] >= 0``, what row ``sources[j]`` of the step
+        launched before this one chose (``tokens[j]`` is then any valid id).  ``sampler``: the settings of
+        this step's draws (of the kind the graph was captured for); default: the sampler of the capture."""
+        self._fill(slots, tokens, requests, steps, sources, sampler)
         self.stepper.upload(self.host, self.dev)
         if self.graph is None and not self.failed:
             try:
@@ -137,9 +174,9 @@ class GraphedDecode:
             self._forward()
         for s in slots:
             self.stepper.cache.advance(s, 1)
-        return self.loop.read_back(self.B)
+        return self.loop.read_back(len(slots))
 
     def run(self, slots: Sequence[int], tokens: Sequence[int], requests: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
-        """One decode step of ``B`` rows; returns the chosen tokens (int32 [B], device)."""
+        """One decode step; returns the chosen tokens (int32 [B], device; the first ``len(slots)`` count)."""
         self.launch(slots, tokens, requests, steps)
         return self.tokens_out

@@ -41,6 +41,8 @@ class StepLayout:
     pos: int = 0
     row: int = 0
     slots: int = 0
+    first: int = 0
+    lens: int = 0
     want: int = 0
     tables: Optional[List[int]] = None
     total: int = 0
@@ -51,6 +53,8 @@ class StepLayout:
         self.pos = o; o += _pad4(self.T)
         self.row = o; o += _pad4(self.T)
         self.slots = o; o += _pad4(self.B)
+        self.first = o; o += _pad4(self.B + 1)
+        self.lens = o; o += _pad4(self.B)
         self.want = o; o += _pad4(max(self.W, 1))
         self.tables = []
         for w in self.widths:
@@ -94,13 +98,16 @@ class Stepper:
         B = len(slots)
         if B == 0:
             raise StepError("a step needs at least one sequence")
-        if len(set(slots)) != B:
+        live = [s for s in slots if s != cache.idle_slot]        # idle rows (padding of a fixed-size step) may repeat
+        if len(set(live)) != len(live):
             raise StepError("a sequence appears twice in one step")
         lens = [int(n) for n in lens]
         starts = [cache.length(s) for s in slots]
         for b, n in enumerate(lens):
             if n < 1:
                 raise StepError(f"row {b} brings no token")
+            if slots[b] == cache.idle_slot and n != 1:
+                raise StepError(f"row {b} is idle and brings {n} tokens; an idle row brings one")
             if starts[b] + n > self.max_context:
                 raise StepError(f"row {b} would reach {starts[b] + n} tokens; the engine was set up for sequences "
                                 f"of at most {self.max_context}")
@@ -108,7 +115,7 @@ class Stepper:
             want = [[n - 1] for n in lens]
         T = sum(lens)
         W = sum(len(w) for w in want)
-        for s, n in zip(slots, lens):
+        for s, n in zip(live, (n for s, n in zip(slots, lens) if s != cache.idle_slot)):
             cache.reserve(s, n)
         if widths is None:
             widths = [max(pages_for(st + n) for st, n in zip(starts, lens))] * len(cache.groups)
@@ -127,6 +134,8 @@ class Stepper:
                     raise StepError(f"row {b} has a token outside the vocabulary of {self.vocab}")
                 host[lay.ids + a: lay.ids + e] = ids
         host[lay.slots: lay.slots + B] = np.asarray(slots, dtype=np.int32)
+        host[lay.first: lay.first + B + 1] = cu
+        host[lay.lens: lay.lens + B] = np.asarray(lens, dtype=np.int32)
         w_at = lay.want
         for b, places in enumerate(want):
             for p in places:
@@ -145,7 +154,8 @@ class Stepper:
         return StepContext(
             T=lay.T, B=lay.B, dtype=self.model.dtype, device=self.device,
             tok_pos=dev[lay.pos: lay.pos + lay.T], tok_row=dev[lay.row: lay.row + lay.T],
-            slots=dev[lay.slots: lay.slots + lay.B], slot_ids=list(slot_ids), lens=list(lens), starts=list(starts),
+            slots=dev[lay.slots: lay.slots + lay.B], row_first=dev[lay.first: lay.first + lay.B + 1],
+            row_lens=dev[lay.lens: lay.lens + lay.B], slot_ids=list(slot_ids), lens=list(lens), starts=list(starts),
             one_token_each=all(n == 1 for n in lens), cache=self.cache, tables=tables,
             max_context=max(s + n for s, n in zip(starts, lens)))
 

@@ -206,9 +206,19 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     return out
 
 
+def sample_settings_words(temperature: float, top_k: int, top_p: float, seed: int):
+    """The six int32 words of the sampler's settings as the kernels read them from device memory."""
+    import struct
+    return list(struct.unpack("<6i", struct.pack("<fifiQ", float(temperature), int(top_k), float(top_p), 0,
+                                                 int(seed) & ((1 << 64) - 1))))
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, request: torch.Tensor,
-           step: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One draw per row of float32 logits [B, V]; row b uses the uniform of (seed, request[b], step[b])."""
+           step: torch.Tensor, out: Optional[torch.Tensor] = None, settings: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One draw per row of float32 logits [B, V]; row b uses the uniform of (seed, request[b], step[b]).
+    ``settings`` (int32 [6] on the device, ``sample_settings_words``): where given, the kernels read
+    temperature, top_k, top_p and the seed from there at run time (a captured launch then follows settings
+    that change); the arguments still decide which passes run, i.e. whether there is a cut by rank and by mass."""
     B, V = logits.shape
     _need(logits, "logits", torch.float32)
     _need(request, "request", torch.int32, (B,)); _need(step, "step", torch.int32, (B,))
@@ -221,8 +231,13 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
     lib = core()
     ws = scratch("sample.state", lib.pe_sample_scratch_bytes(B, V), logits.device, zeroed=True)
     cut_k, cut_p = 0 < top_k < V, top_p < 1.0
+    if settings is not None:
+        _need(settings, "settings", torch.int32, (6,))
+        if settings.data_ptr() % 8:
+            raise KernelError("settings must start on an 8-byte boundary")
     check(lib.pe_sample(logits.data_ptr(), out.data_ptr(), B, V, float(temperature), int(top_k), float(top_p),
-                        int(seed) & ((1 << 64) - 1), request.data_ptr(), step.data_ptr(), ws.data_ptr(), stream_ptr()),
+                        int(seed) & ((1 << 64) - 1), request.data_ptr(), step.data_ptr(), ws.data_ptr(), _ptr(settings),
+                        stream_ptr()),
           "sample", 2 + 3 * cut_k + 3 * cut_p)
     return out
 
@@ -506,7 +521,10 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
     return q
 
 
-# ---------------------------------------------------------------------------- tcgen05 products for many rows (bfloat16)
+# ---------------------------------------------------------------------------- tcgen05 products for more than 16 rows (bfloat16)
+
+ORIENTATION = {None: 0, "rows": 1, "swapped": 2, "pairs": 3}
+
 
 def gemm_tcgen05_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
@@ -514,10 +532,14 @@ def gemm_tcgen05_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                 accumulate_into: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+                 accumulate_into: Optional[torch.Tensor] = None, swiglu: bool = False,
+                 orientation: Optional[str] = None) -> torch.Tensor:
     """a [M, K] . w [N, K]^T on the tcgen05 tensor cores with a fused epilogue: bfloat16 result
     (+ bias); or added into the float32 tensor ``accumulate_into``; or, with ``swiglu`` and
-    w = [gate rows; up rows], silu(gate) * up as bfloat16 [M, N / 2]."""
+    w = [gate rows; up rows], silu(gate) * up as bfloat16 [M, N / 2].  ``orientation``: "rows" puts
+    the rows of ``a`` on the accumulator's lanes, "pairs" the same with 256 rows to a pair of CTAs
+    (``cta_group::2``), "swapped" the rows of ``w`` (for up to a few hundred rows of ``a``); None
+    chooses by M."""
     M, K = a.shape
     N = w.shape[0]
     _need(a, "a", torch.bfloat16); _need(w, "w", torch.bfloat16, (N, K))
@@ -531,6 +553,44 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     else:
         out, epilogue = torch.empty(M, N, dtype=torch.bfloat16, device=a.device), 0
     check(core().pe_gemm_tcgen05(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
-                                 out.data_ptr(), epilogue, M, N, K, status_ptr(a.device), stream_ptr()),
-          "gemm_tcgen05")
+                                 out.data_ptr(), epilogue, M, N, K, ORIENTATION[orientation], status_ptr(a.device),
+                                 stream_ptr()), "gemm_tcgen05")
     return out
+
+
+GEMM_ROPE_HEAD_DIMS = (16, 32, 64, 128)      # a 128-row tile of the weight holds whole heads
+
+
+def gemm_qkv_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], n_q: int, n_kv: int,
+                        head_dim: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], tok_pos: torch.Tensor,
+                        tok_row: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                        block_table: Optional[torch.Tensor], table_stride: int,
+                        orientation: Optional[str] = None) -> torch.Tensor:
+    """Rotated queries [M, n_q * head_dim] of bfloat16 rows ``a`` [M, K]: the q/k/v product with bias, the
+    rotation of q and k and the write of keys and values into their cache pages in one tcgen05 kernel
+    (the cache write is skipped when ``k_pool`` is None)."""
+    M, K = a.shape
+    N = (n_q + 2 * n_kv) * head_dim
+    _need(a, "a", torch.bfloat16); _need(w_qkv, "w_qkv", torch.bfloat16, (N, K))
+    if head_dim not in GEMM_ROPE_HEAD_DIMS:
+        raise KernelError(f"head size {head_dim} is not taken by the fused q/k/v product: {GEMM_ROPE_HEAD_DIMS} are")
+    if b_qkv is not None:
+        _need(b_qkv, "b_qkv", None, (N,))
+    _need(tok_pos, "tok_pos", torch.int32, (M,)); _need(tok_row, "tok_row", torch.int32, (M,))
+    if cos is not None:
+        _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32, cos.shape)
+        if cos.shape[1] != head_dim // 2:
+            raise KernelError("cos/sin tables need head_dim/2 columns")
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+        _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim):
+            raise KernelError(f"cache pool must be [pages, {n_kv}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
+    q = torch.empty(M, n_q * head_dim, dtype=torch.bfloat16, device=a.device)
+    check(core().pe_gemm_tcgen05_rope(a.data_ptr(), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
+                                      q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
+                                      tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
+                                      1 if store else 0, ORIENTATION[orientation], status_ptr(a.device), stream_ptr()),
+          "gemm_qkv_rope_store")
+    return q

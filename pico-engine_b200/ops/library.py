@@ -27,10 +27,11 @@ _SIGNATURES = {
     "pe_linear_simt": [P, I, P, I, P, I, P, I, I, I, I, P],
     "pe_attention_generic": [P, I, P, P, P, I, P, I, P, P, I, I, I, I, I, F, P],
     "pe_argmax": [P, P, I, I, P, P],
-    "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P, P],
+    "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P, P, P],
     "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
     "pe_linear_mma_splits": [I, I],
-    "pe_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, P, P],
+    "pe_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, P, P],
+    "pe_gemm_tcgen05_rope": [P, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P, P],
     "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
     "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
     "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],

@@ -68,12 +68,31 @@ class GQAAttention(Mixer):
         return CacheNeeds(kv=KVNeed(s.n_kv_heads, s.head_dim, s.window))
 
     def _attend(self, h, ctx, cache_entry, owns_cache):
+        from ..ops.linear import qkv_rope_store, qkv_rope_store_takes
+        from .position import NoPosition, RotaryHalf
         s = self.spec
-        qkv = linear(h, self.w_qkv, self.b_qkv, out_dtype=ctx.dtype)
         kv = ctx.kv(cache_entry)
+        if type(self.position) in (RotaryHalf, NoPosition) and qkv_rope_store_takes(h, self.w_qkv, self.b_qkv, s.head_dim):
+            # many rows in bfloat16: projection, bias, rotation and cache write can be one tcgen05 kernel
+            cos, sin = self._tables(ctx)
+            q = qkv_rope_store(h, self.w_qkv, self.b_qkv, s.n_heads, s.n_kv_heads, s.head_dim, cos, sin, ctx.tok_pos,
+                               ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None, kv.table, kv.stride)
+            if q is not None:
+                return kernels.attention(q, q.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table,
+                                         kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
+        qkv = linear(h, self.w_qkv, self.b_qkv, out_dtype=ctx.dtype)
         self.position.rotate_and_store(qkv, s.n_heads, s.n_kv_heads, s.head_dim, ctx, kv if owns_cache else None)
         return kernels.attention(qkv, qkv.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table,
                                  kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
+
+    def _tables(self, ctx):
+        """The rotary tables of this layer's position encoding (None, None where it has none), checked
+        against the longest sequence of the step."""
+        cos, sin = getattr(self.position, "cos", None), getattr(self.position, "sin", None)
+        if cos is not None and ctx.max_context > cos.shape[0]:
+            raise ValueError(f"a sequence reaches position {ctx.max_context - 1}, the rotary tables hold "
+                             f"{cos.shape[0]} positions")
+        return cos, sin
 
     def apply(self, h, ctx, entry, cache_entry, owns_cache):
         return linear(self._attend(h, ctx, cache_entry, owns_cache), self.w_o, out_dtype=ctx.dtype)
@@ -94,10 +113,7 @@ class GQAAttention(Mixer):
             ctx.settle(x)
             s = self.spec
             kv = ctx.kv(cache_entry)
-            cos, sin = getattr(self.position, "cos", None), getattr(self.position, "sin", None)
-            if cos is not None and ctx.max_context > cos.shape[0]:
-                raise ValueError(f"a sequence reaches position {ctx.max_context - 1}, the rotary tables hold "
-                                 f"{cos.shape[0]} positions")
+            cos, sin = self._tables(ctx)
             q = kernels.norm_qkv_rope_store(x, norm.weight, norm.eps, self.w_qkv, self.b_qkv, s.n_heads, s.n_kv_heads,
                                             s.head_dim, cos, sin, ctx.tok_pos, ctx.tok_row,
                                             kv.k if owns_cache else None, kv.v if owns_cache else None, kv.table, kv.stride)

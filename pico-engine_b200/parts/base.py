@@ -42,7 +42,12 @@ class StepContext:
     """Everything a part may know about the running step.
 
     The step runs ``T`` tokens of ``B`` sequences, packed sequence after sequence.  Token t
-    belongs to batch row ``tok_row[t]`` and stands at position ``tok_pos[t]`` of its sequence.
+    belongs to batch row ``tok_row[t]`` and stands at position ``tok_pos[t]`` of its sequence; row b's
+    tokens are ``row_first[b] .. row_first[b + 1] - 1``.  The device arrays are what a kernel needs to
+    find its rows, also inside a captured graph, where the host lists (``lens``, ``starts``,
+    ``slot_ids``) are those of the step that was captured and must not be read.  A captured step
+    of a fixed number of rows may carry idle rows: they bring one token at position 0 of the cache's idle
+    slot, and nobody reads what they produce.
     """
     T: int
     B: int
@@ -51,7 +56,9 @@ class StepContext:
     tok_pos: torch.Tensor                 # int32 [T], device
     tok_row: torch.Tensor                 # int32 [T], device
     slots: torch.Tensor                   # int32 [B], device: sequence slot of each batch row
-    slot_ids: List[int]                   # the same on the host
+    row_first: torch.Tensor               # int32 [B + 1], device: packed index of each row's first token; row_first[B] = T
+    row_lens: torch.Tensor                # int32 [B], device: tokens each row brings in this step
+    slot_ids: List[int]                   # the slots on the host
     lens: List[int]                       # tokens of each row in this step (host)
     starts: List[int]                     # position of each row's first token (host)
     one_token_each: bool                  # every row brings exactly one token

@@ -31,7 +31,8 @@ class SwiGLU(FeedForward):
         self.w_down = get(s.prefix + s.down_name + ".weight")
 
     def _activation(self, h, ctx):
-        return kernels.swiglu(linear(h, self.w_gate_up, out_dtype=ctx.dtype))
+        from ..ops.linear import gate_up_swiglu
+        return gate_up_swiglu(h, self.w_gate_up)
 
     def apply(self, h, ctx):
         return linear(self._activation(h, ctx), self.w_down, out_dtype=ctx.dtype)

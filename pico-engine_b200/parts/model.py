@@ -54,8 +54,8 @@ class DecoderModel:
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> List[Optional[CacheNeeds]]:
         """Per schedule entry; None for an entry that reads another entry's cache."""
-        return [None if e.cache_of is not None else self.layers[e.layer].mixer.cache_needs()
-                for e in self.plan.schedule]
+        return [None if e.cache_of is not None or self.layers[e.layer].mixer is None
+                else self.layers[e.layer].mixer.cache_needs() for e in self.plan.schedule]
 
     # ------------------------------------------------------------------ a step
     def hidden(self, token_ids: torch.Tensor, ctx: StepContext) -> torch.Tensor:

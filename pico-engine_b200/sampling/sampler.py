@@ -35,11 +35,19 @@ class Sampler:
     def __init__(self, params: SamplingParams):
         self.params = params
 
+    def kind(self, vocab: int) -> tuple:
+        """What fixes the kernels that a choice launches: (greedy, a cut by rank, a cut by mass).  Samplers of
+        one kind differ in numbers only (temperature, k, p, seed), which a captured launch reads at run time."""
+        p = self.params
+        return (True, False, False) if p.greedy else (False, 0 < p.top_k < vocab, p.top_p < 1.0)
+
     def choose(self, logits: torch.Tensor, request: torch.Tensor, step: torch.Tensor,
-               out: torch.Tensor | None = None) -> torch.Tensor:
+               out: torch.Tensor | None = None, settings: torch.Tensor | None = None) -> torch.Tensor:
         """int32 [B] next tokens for float32 logits [B, V].  Row b draws with the uniform of
-        (seed, request[b], step[b]); greedy choice ignores both."""
+        (seed, request[b], step[b]); greedy choice ignores both.  ``settings``: int32 [6] on the device
+        (``kernels.sample_settings_words``) from which the kernels take temperature, top-k, top-p and seed
+        instead of from this sampler's parameters, which then only say which kind of choice it is."""
         p = self.params
         if p.greedy:
             return kernels.argmax(logits, out)
-        return kernels.sample(logits, p.temperature, p.top_k, p.top_p, p.seed, request, step, out)
+        return kernels.sample(logits, p.temperature, p.top_k, p.top_p, p.seed, request, step, out, settings)

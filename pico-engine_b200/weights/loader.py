@@ -7,6 +7,7 @@ whole comparison is made first and reported in one error.
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Callable, Dict, Tuple
 
@@ -32,6 +33,10 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class UnusedWeightsWarning(UserWarning):
+    """The checkpoint holds tensors that the model does not use; they are named and left unread."""
+
+
 @dataclass(frozen=True)
 class ParamSpec:
     """What a part expects of one tensor.  ``init`` names the distribution of the
@@ -41,13 +46,20 @@ class ParamSpec:
 
 
 def check(expected: Dict[str, ParamSpec], stored: Dict[str, Tuple[int, ...]], ignorable=(), where="the checkpoint"):
-    """Raise one :class:`WeightError` naming every missing, unexpected and mis-shaped tensor."""
+    """A checkpoint that lacks a tensor or holds one in another shape is refused with one
+    :class:`WeightError` that names every missing, unexpected and mis-shaped tensor.  A checkpoint that
+    is complete but carries tensors nobody asks for (older conversions store ``rotary_emb.inv_freq``;
+    pico-engine looks tensors up by name and never notices extras, src/pico_engine/model.py:86-97) loads
+    with one :class:`UnusedWeightsWarning` that lists them."""
     missing = sorted(n for n in expected if n not in stored)
     unexpected = sorted(n for n in stored if n not in expected and n not in ignorable)
     wrong = sorted((n, tuple(stored[n]), tuple(expected[n].shape)) for n in expected
                    if n in stored and tuple(stored[n]) != tuple(expected[n].shape))
-    if missing or unexpected or wrong:
+    if missing or wrong:
         raise WeightError(missing, unexpected, wrong, where)
+    if unexpected:
+        warnings.warn(f"weights in {where}: {len(unexpected)} tensor(s) are not used by the model and are left "
+                      f"unread: " + ", ".join(unexpected), UnusedWeightsWarning, stacklevel=3)
 
 
 def convert(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

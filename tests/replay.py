@@ -57,6 +57,61 @@ def batched(requests: dict, batch_size: int, prompt_fraction: float = 0.5) -> li
     return steps
 
 
+def scheduled(requests: dict, plan: dict) -> list:
+    """The general cut.  ``plan[id] = (first step, [tokens brought in each of its steps])``: a request
+    joins at its first step and brings the listed numbers of tokens in consecutive steps, so one
+    step can carry a fresh prompt, a later piece of another prompt and single tokens side by side.
+    Every position is wanted."""
+    at = {r: 0 for r in requests}
+    last = max(first + len(cuts) for first, cuts in plan.values())
+    steps = []
+    for k in range(last):
+        entries, done = [], []
+        for r, (first, cuts) in plan.items():
+            if first <= k < first + len(cuts):
+                n = cuts[k - first]
+                entries.append({"id": r, "tokens": requests[r][at[r]:at[r] + n], "want": list(range(n))})
+                at[r] += n
+                if k == first + len(cuts) - 1:
+                    done.append(r)
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": done})
+    assert all(at[r] == len(requests[r]) for r in requests), "the plan does not cover every token"
+    return steps
+
+
+def pieces(requests: dict, fractions=(0.45, 0.35, 0.2)) -> list:
+    """All requests start together and bring their prompts in pieces of unequal size (the later
+    pieces start inside the sequence and have several tokens)."""
+    plan = {}
+    for i, (r, toks) in enumerate(requests.items()):
+        n = len(toks)
+        fr = fractions[i % len(fractions):] + fractions[:i % len(fractions)]      # every request is cut elsewhere
+        cuts, left = [], n
+        for f in fr[:-1]:
+            c = min(left, max(1, int(n * f)))
+            if c:
+                cuts.append(c)
+                left -= c
+        if left:
+            cuts.append(left)
+        plan[r] = (0, cuts)
+    return scheduled(requests, plan)
+
+
+def mixed(requests: dict) -> list:
+    """Steps that carry a whole prompt, a piece of one and single tokens side by side: request i
+    joins at step i, brings most of its tokens in one or two pieces and the rest one by one."""
+    plan = {}
+    for i, (r, toks) in enumerate(requests.items()):
+        n = len(toks)
+        singles = min(n - 1, 2 + i)
+        head = n - singles
+        cuts = [head] if head < 4 or i % 2 == 0 else [head - head // 3, head // 3]
+        plan[r] = (i, cuts + [1] * singles)
+    return scheduled(requests, plan)
+
+
 def max_tokens_of(steps: list) -> int:
     """The most tokens live requests hold at any time, each rounded up to 64."""
     held, peak = {}, 0

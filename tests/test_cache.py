@@ -31,11 +31,32 @@ def needs(window=None, layers=3, state=0):
 def test_groups_have_storage_of_their_own():
     c = Cache(needs(window=32) + [None], max_tokens=512, max_seqs=4, dtype=torch.float32, device="cpu")
     assert len(c.groups) == 2 and c.groups[0].entries == [0] and c.groups[1].entries == [1, 2]
-    assert c.groups[0].k.shape == (1, 8, 2, PAGE, 16) and c.groups[1].v.shape == (2, 8, 2, PAGE, 16)
+    # 8 pages for the sequences and the idle page behind them
+    assert c.groups[0].k.shape == (1, 9, 2, PAGE, 16) and c.groups[1].v.shape == (2, 9, 2, PAGE, 16)
     assert c.groups[0].k.data_ptr() != c.groups[1].k.data_ptr()
     k, v = c.pools(2)
-    assert k.shape == (8, 2, PAGE, 16) and k.data_ptr() == c.groups[1].k[1].data_ptr()
+    assert k.shape == (9, 2, PAGE, 16) and k.data_ptr() == c.groups[1].k[1].data_ptr()
     assert 3 not in c.group_of
+
+
+def test_idle_rows_take_nothing_from_the_sequences():
+    """The idle slot and page (what the padding rows of a fixed-size step use) lie behind the slots and pages
+    of the sequences: they are never handed out, hold no length, and may stand in a page table many times."""
+    c = Cache(needs(window=32, state=4), max_tokens=128, max_seqs=2, dtype=torch.float32, device="cpu")
+    assert c.idle_slot == 2 and c.idle_page == 2 and c.state[0].shape == (3, 4)
+    a, b = c.open(), c.open()
+    assert {a, b} == {0, 1} and c.length(c.idle_slot) == 0
+    c.reserve(a, 64); c.reserve(b, 64)
+    with pytest.raises(CacheFull):
+        c.reserve(a, 65)
+    table = c.page_table(0, [a, c.idle_slot, c.idle_slot, b], 2)
+    assert table.tolist() == [[0, -1], [2, -1], [2, -1], [1, -1]]
+    assert c.page_table(1, [c.idle_slot]).tolist() == [[2]]
+    snap = c.snapshot_state()
+    c.state[0][a].fill_(7.0)
+    c.restore_state(snap)
+    assert float(c.state[0].abs().sum()) == 0.0
+    c.close(a); c.close(b); c.check()
 
 
 def test_each_sequence_has_its_own_length_and_pages():
@@ -92,7 +113,7 @@ def test_window_group_gives_pages_back_as_the_window_moves():
 
 def test_state_is_zero_when_a_slot_is_taken():
     c = Cache(needs(state=5), max_tokens=128, max_seqs=2, dtype=torch.float32, device="cpu")
-    assert c.state_entries == [0] and c.state_of(0).shape == (2, 5) and c.state_of(1) is None
+    assert c.state_entries == [0] and c.state_of(0).shape == (3, 5) and c.state_of(1) is None     # two sequences and the idle row
     s = c.open()
     c.state_of(0)[s] += 3.0
     c.close(s)

@@ -64,6 +64,62 @@ def test_unequal_batches_one_after_another(models, name, dtype, batch_size, frac
     replay.compare(replay.run_in_process(eng, steps), replay.plain_logits(cfg, w, reqs), dtype, "batched")
 
 
+def many_short_requests(cfg, name, n, seed):
+    """``n`` requests of 2 to 40 tokens, a few of them longer than the window where there is one."""
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(2, 41, (n,), generator=g).tolist()
+    for i, extra in zip(range(3, n, 11), ({"A": 0, "B": 45, "C": 110}[name],) * n):
+        lengths[i] += extra
+    return random_requests(cfg, lengths, seed + 1)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("batch_size", [24, 64])
+def test_one_token_steps_of_many_rows(models, name, dtype, batch_size):
+    """Batches of 24 and 64 requests: their one-token steps have 17 to 64 rows, which take other
+    matrix products than the steps of a few rows; requests end one by one, so every row count from
+    the batch size down is run, and the second batch reuses the first one's slots."""
+    eng, cfg, w = models[(name, dtype)]
+    reqs = many_short_requests(cfg, name, batch_size + 9, 30 + batch_size)
+    steps = replay.batched(reqs, batch_size, 0.5)
+    assert max(len(s["entries"]) for s in steps[1:]) == batch_size
+    replay.compare(replay.run_in_process(eng, steps), replay.plain_logits(cfg, w, reqs), dtype, f"batched by {batch_size}")
+
+
+PIECE_LENGTHS = {"A": [100, 7, 64, 33, 128], "B": [200, 9, 130, 64, 256], "C": [300, 20, 150, 257, 129]}
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_prompts_in_pieces(models, name, dtype):
+    """A prompt brought in two or three steps: the later pieces start inside the sequence and bring several
+    tokens.  On B and C (windows of 32 and 70) the first piece of the long requests is longer than a
+    page plus the window, so the windowed group has given pages back before the next piece arrives
+    and that piece attends over a page table with holes."""
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, PIECE_LENGTHS[name], 40)
+    steps = replay.pieces(reqs)
+    assert any(len(e["tokens"]) > 1 for s in steps[1:] for e in s["entries"])
+    replay.compare(replay.run_in_process(eng, steps), replay.plain_logits(cfg, w, reqs), dtype, "pieces")
+    if name != "A":                                      # the holes are really there
+        eng.ensure_cache(1024, cfg["max_position_embeddings"], max_seqs=4)
+        slot = eng.cache.open()
+        eng.stepper.step([slot], [reqs["r0"][:len(reqs["r0"]) // 2]], [[]])
+        windowed = [g for g in eng.cache.groups if g.need.window is not None]
+        assert windowed and windowed[0].table[slot][0] == -1
+        eng.cache.close(slot)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_mixed_steps(models, name, dtype):
+    """One step carries a fresh prompt, a piece of another and single tokens of others."""
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, PIECE_LENGTHS[name][::-1] + [12, 3], 41)
+    steps = replay.mixed(reqs)
+    kinds = [sorted({"one" if len(e["tokens"]) == 1 else "many" for e in s["entries"]}) for s in steps]
+    assert ["many", "one"] in kinds
+    replay.compare(replay.run_in_process(eng, steps), replay.plain_logits(cfg, w, reqs), dtype, "mixed")
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_cutting_does_not_change_float32_results_beyond_rounding(models, name, dtype):
     eng, cfg, w = models[(name, dtype)]
@@ -176,7 +232,7 @@ def test_stop_tokens_and_many_batches(models, name):
     assert not eng.cache.lengths and eng.cache.slots.free_count == eng.cache.max_seqs
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_greedy_generation_bfloat16(models, name, use_graph):
     """Each chosen token must be a (near) maximum of the plain logits for the engine's own
@@ -195,7 +251,7 @@ def test_greedy_generation_bfloat16(models, name, use_graph):
     assert exact >= 40
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_decoding_one_step_ahead_changes_no_token(models, name):
     """With graphs the loop launches a step before it has read the one in flight; without, it does
     not.  Budgets that differ, stop tokens that fall early, late and on the last token, sampling."""
@@ -213,12 +269,49 @@ def test_decoding_one_step_ahead_changes_no_token(models, name):
     assert not eng.cache.lengths and eng.cache.slots.free_count == eng.cache.max_seqs
 
 
-def test_graph_and_eager_decode_agree(models):
-    eng, cfg, w = models[("B", "bfloat16")]
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_graph_and_eager_decode_agree(models, name):
+    eng, cfg, w = models[(name, "bfloat16")]
     prompts = list(random_requests(cfg, [20, 70, 3], 20).values())
     a = eng.generate(prompts, max_tokens=70, temperature=0.7, top_p=0.9, seed=3, use_graph=True)
     b = eng.generate(prompts, max_tokens=70, temperature=0.7, top_p=0.9, seed=3, use_graph=False)
     assert a == b
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "float32"), ("C", "bfloat16")])
+def test_many_requests_share_a_few_graphs(models, name, dtype):
+    """64 requests whose budgets differ end one by one, so the decode steps have every row count from 64 down:
+    they run in the graphs of a few row buckets (idle rows fill a bucket), with the tokens of eager decoding.
+    Other temperatures and seeds are numbers that a graph reads at run time: they capture nothing new."""
+    eng, cfg, w = models[(name, dtype)]
+    g = torch.Generator().manual_seed(31)
+    lengths = torch.randint(2, 13, (64,), generator=g).tolist()
+    prompts = list(random_requests(cfg, lengths, 32).values())
+    budgets = [1 + (5 * i) % 23 for i in range(64)]
+    eng._graphs.clear()
+    graphed = eng.generate(prompts, max_tokens=budgets, temperature=0.0, use_graph=True, stop_token_ids=())
+    assert 3 <= len(eng._graphs) <= 7, sorted(eng._graphs)
+    eager = eng.generate(prompts, max_tokens=budgets, temperature=0.0, use_graph=False, stop_token_ids=())
+    assert [len(o) for o in graphed] == budgets
+    if dtype == "float32":
+        assert graphed == eager
+        for i in (0, 17, 63):
+            assert graphed[i] == plain.generate(cfg, w, prompts[i], budgets[i])
+    else:                                               # bfloat16: rows of a bucket of 64 and of 16 take different kernels
+        for p, out in zip(prompts, graphed):
+            logits = plain.forward(cfg, w, p + out)
+            for i, tok in enumerate(out):
+                row = logits[len(p) + i - 1]
+                assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max())), (i, tok)
+    kw = dict(max_tokens=6, top_k=0, top_p=1.0, stop_token_ids=())
+    first = eng.generate(prompts[:8], temperature=0.8, seed=1, use_graph=True, **kw)
+    held = len(eng._graphs)
+    second = eng.generate(prompts[:8], temperature=0.5, seed=2, use_graph=True, **kw)
+    third = eng.generate(prompts[:8], temperature=0.8, seed=1, use_graph=True, **kw)
+    assert len(eng._graphs) == held and third == first and second != first
+    if dtype == "float32":
+        assert second == eng.generate(prompts[:8], temperature=0.5, seed=2, use_graph=False, **kw)
+        assert second == [plain.generate(cfg, w, p, 6, temperature=0.5, seed=2, request=i) for i, p in enumerate(prompts[:8])]
 
 
 def test_weights_stored_in_float32_stay_so(tmp_path):

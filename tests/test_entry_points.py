@@ -81,3 +81,74 @@ def test_kernel_library_refuses_to_run_without_a_gpu():
         require_cuda("cpu")
     with pytest.raises(KernelError, match="no CUDA device"):
         require_cuda("cuda")
+
+
+def test_command_line_refuses_bad_random_arguments(tmp_path):
+    def run(*args):
+        return subprocess.run([sys.executable, "-m", "pico_engine", *args], cwd=ROOT, capture_output=True, text=True)
+    r = run("--random-config", "qwen9", "--prompt", "1")
+    assert r.returncode != 0 and "unknown shape" in r.stderr
+    r = run(str(tmp_path), "--random-config", "tiny-a", "--prompt", "1")
+    assert r.returncode != 0 and "model folder or --random-config" in r.stderr
+    r = run("--random-config", "tiny-a", "--random-prompt", "0")
+    assert r.returncode != 0 and "positive lengths" in r.stderr
+    r = run("--random-config", "tiny-a", "--layers", "0", "--prompt", "1")
+    assert r.returncode != 0 and "--layers" in r.stderr
+
+
+def test_random_prompts_are_seeded():
+    from pico_engine.__main__ import random_prompts
+    a, b = random_prompts([5, 9], 256, 3), random_prompts([5, 9], 256, 3)
+    assert a == b and [len(p) for p in a] == [5, 9] and all(0 <= t < 256 for p in a for t in p)
+    assert random_prompts([5, 9], 256, 4) != a
+
+
+# ---------------------------------------------------------------------------- the command lines on a GPU
+
+def _outputs(stdout: str):
+    return [json.loads(line) for line in stdout.splitlines() if line.startswith("{")]
+
+
+@pytest.mark.gpu
+def test_command_line_generates_the_plain_tokens(tmp_path):
+    """``python -m pico_engine FOLDER --prompt ... --prompt ... --temperature 0`` prints the token ids that
+    the plain implementation chooses (float32, so that the comparison is exact), stops at a stop token, and
+    the same model drawn at random from its name gives tokens too."""
+    import plain_qwen2 as plain
+    from conftest import TINY_B, make_weights, write_model
+    cfg = dict(TINY_B)
+    w = make_weights(cfg, 1, sharp=True)
+    folder = write_model(tmp_path / "m", cfg, w)
+    prompts = [[3, 1, 4, 1, 5, 9, 2, 6], [27, 18, 28]]
+    base = [sys.executable, "-m", "pico_engine", folder, "--prompt", "3,1,4,1,5,9,2,6", "--prompt", "27 18 28",
+            "--max-tokens", "7", "--temperature", "0", "--dtype", "float32"]
+    r = subprocess.run(base, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    outs = _outputs(r.stdout)
+    want = [plain.generate(cfg, w, p, 7) for p in prompts]
+    assert [o["prompt"] for o in outs] == prompts and [o["output"] for o in outs] == want
+    assert "[engine] loaded in" in r.stdout and "tok/s" in r.stdout
+    stop = want[0][3]
+    r = subprocess.run(base + ["--stop-token-ids", str(stop), "--no-graph"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [o["output"] for o in _outputs(r.stdout)] == [plain.generate(cfg, w, p, 7, stop=(stop,)) for p in prompts]
+    r = subprocess.run([sys.executable, "-m", "pico_engine", "--random-config", "tiny-a", "--random-prompt", "5,9,13",
+                        "--max-tokens", "8", "--temperature", "0.8", "--seed", "4"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    outs = _outputs(r.stdout)
+    assert [len(o["prompt"]) for o in outs] == [5, 9, 13] and all(len(o["output"]) == 8 for o in outs)
+
+
+@pytest.mark.gpu
+def test_benchmark_command_line_writes_its_record(tmp_path):
+    out = tmp_path / "record.json"
+    r = subprocess.run([sys.executable, "-m", "pico_engine.benchmark", "--random", "tiny-a", "--batch", "1,3", "--context", "96",
+                        "--prefill", "64", "--n-tokens", "8", "--warmups", "1", "--repetitions", "2", "--output", str(out)],
+                       cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rec = json.loads(out.read_text())
+    assert rec["prefill"]["tokens"] == 64 and rec["prefill"]["ms"] > 0
+    for b in ("1", "3"):
+        s = rec["decode"][b]["tokens_per_s"]
+        assert s["n"] == 2 and 0 < s["p10"] <= s["median"] <= s["p90"]
+    assert "decode batch 3" in r.stdout

@@ -42,6 +42,28 @@ def test_window_rule_by_hand():
     assert plain.layer_window(TINY_A, 1) is None
 
 
+def test_windowed_attention_against_loops_written_out():
+    """plain.attention with a window against the definition spelled out token by token (query p sees key j iff
+    0 <= p - j < window; query head h reads key/value head h // group): no mask helper, no batched product."""
+    L, nh, nkv, hd, window = 11, 4, 2, 6, 4
+    g = torch.Generator().manual_seed(7)
+    q, k, v = (torch.randn(L, n, hd, generator=g, dtype=torch.float64) for n in (nh, nkv, nkv))
+    want = torch.zeros(L, nh, hd, dtype=torch.float64)
+    for p in range(L):
+        for h in range(nh):
+            kvh = h // (nh // nkv)
+            keys = [j for j in range(L) if 0 <= p - j < window]
+            assert keys == list(range(max(0, p - window + 1), p + 1))
+            scores = [sum(float(q[p, h, d]) * float(k[j, kvh, d]) for d in range(hd)) / math.sqrt(hd) for j in keys]
+            top = max(scores)
+            e = [math.exp(x - top) for x in scores]
+            for j, wgt in zip(keys, e):
+                want[p, h] += wgt / sum(e) * v[j, kvh]
+    got = plain.attention(q.float(), k.float(), v.float(), window).view(L, nh, hd)
+    assert torch.allclose(got.double(), want, atol=1e-5)
+    assert not torch.allclose(plain.attention(q.float(), k.float(), v.float(), None).view(L, nh, hd).double(), want, atol=1e-2)
+
+
 def test_window_changes_only_positions_beyond_it():
     w = make_weights(TINY_B, 1, sharp=True)
     ids = torch.randint(0, 512, (50,), generator=torch.Generator().manual_seed(3)).tolist()

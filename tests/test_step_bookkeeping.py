@@ -13,7 +13,7 @@ from pico_engine.parts.block import pre_norm
 
 def context():
     z = torch.zeros(0, dtype=torch.int32)
-    return base.StepContext(T=3, B=1, dtype=torch.float32, device=torch.device("cpu"), tok_pos=z, tok_row=z, slots=z,
+    return base.StepContext(T=3, B=1, dtype=torch.float32, device=torch.device("cpu"), tok_pos=z, tok_row=z, slots=z, row_first=z, row_lens=z,
                             slot_ids=[0], lens=[3], starts=[0], one_token_each=False, cache=None)
 
 

@@ -69,6 +69,18 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert word in text
 
 
+def test_tensors_nobody_asks_for_are_a_warning_that_names_them(tmp_path):
+    """A complete checkpoint with extra tensors (older conversions store rotary_emb.inv_freq) loads."""
+    from pico_engine.weights import UnusedWeightsWarning
+    w = make_weights(TINY_A, 0)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    w["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    model = DecoderModel(config_from_dict(TINY_A).plan(), torch.float32, "cpu")
+    with pytest.warns(UnusedWeightsWarning, match=r"2 tensor\(s\).*layers\.0\.self_attn\.rotary_emb\.inv_freq, model\.layers\.1"):
+        load_folder(model, write_model(tmp_path / "m", TINY_A, w))
+    assert torch.equal(model.embedding, w["model.embed_tokens.weight"])
+
+
 def test_tied_model_may_carry_a_head_it_does_not_use(tmp_path):
     w = make_weights(TINY_A, 0)
     w["lm_head.weight"] = w["model.embed_tokens.weight"].clone()
