@@ -14,7 +14,6 @@ import argparse
 import json
 import os
 import sys
-import threading
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -34,59 +33,6 @@ def peaks() -> tuple[dict, str]:
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
-
-
-class ClockSampler:
-    """Reads SM clocks and throttle reasons through NVML while the timed region runs (reading only)."""
-
-    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
-               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
-               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
-
-    def __init__(self, index: int = 0, period_s: float = 0.02):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self.period_s, self._stop, self._thread, self._h, self._nvml = period_s, threading.Event(), None, None, None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nvml = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
-        except Exception:                                   # noqa: BLE001 - no NVML: the record says so
-            self._nvml = None
-
-    def _read(self):
-        n = self._nvml
-        try:
-            self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
-            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
-                else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
-            for bit, name in self.REASONS.items():
-                if bits & bit and name != "gpu_idle":
-                    self.reasons.add(name)
-        except Exception:                                   # noqa: BLE001
-            pass
-
-    def __enter__(self):
-        if self._nvml is not None:
-            def loop():
-                while not self._stop.is_set():
-                    self._read()
-                    self._stop.wait(self.period_s)
-            self._thread = threading.Thread(target=loop, daemon=True)
-            self._thread.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
-
-    def record(self) -> dict:
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable: NVML gave no sample"]}
-        s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
 def reference_arm(steps: int, warmup: int, layers) -> int:
@@ -139,7 +85,7 @@ def main() -> int:
     eng.ensure_cache(64 * CONTEXT, CONTEXT, max_seqs=64)
     pk, pk_kind = peaks()
 
-    with ClockSampler() as clocks:
+    with B.ClockSampler() as clocks:
         main_run = B.decode_device(eng, BATCH, CONTEXT, args.steps, warmup)
     side_steps = min(args.steps, 128)
     b1 = B.decode_device(eng, 1, CONTEXT, side_steps, warmup)

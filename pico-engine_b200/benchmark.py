@@ -13,8 +13,9 @@ from __future__ import annotations
 
 import argparse
 import json
+import threading
 import time
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -38,6 +39,59 @@ def summary(values: Sequence[float]) -> Dict[str, float]:
     """median / p10 / p90 / min / max (pico-engine src/pico_engine/evidence.py:47-56)."""
     return {"median": percentile(values, 50), "p10": percentile(values, 10), "p90": percentile(values, 90),
             "min": float(min(values)), "max": float(max(values)), "n": len(values)}
+
+
+class ClockSampler:
+    """Reads SM clocks and throttle reasons through NVML while the timed region runs (reading only)."""
+
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int = 0, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period_s, self._stop, self._thread, self._h, self._nvml = period_s, threading.Event(), None, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:                                   # noqa: BLE001 - no NVML: the record says so
+            self._nvml = None
+
+    def _read(self):
+        n = self._nvml
+        try:
+            self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
+                else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+            for bit, name in self.REASONS.items():
+                if bits & bit and name != "gpu_idle":
+                    self.reasons.add(name)
+        except Exception:                                   # noqa: BLE001
+            pass
+
+    def __enter__(self):
+        if self._nvml is not None:
+            def loop():
+                while not self._stop.is_set():
+                    self._read()
+                    self._stop.wait(self.period_s)
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def record(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable: NVML gave no sample"]}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
 # ---------------------------------------------------------------------------- work accounting
@@ -187,6 +241,85 @@ def decode_end_to_end(engine, batch: int, context: int, steps: int, use_graph: b
             "h2d_bytes_per_step": t["h2d_bytes"] // max(t["decode_steps"], 1), "d2h_bytes_per_step": 4 * batch}
 
 
+@torch.inference_mode()
+def generate_protocol(engine, n_requests: int, shortest: int, longest: int, steps: int, warmups: int = 1,
+                      repetitions: int = 3, seed: int = 0, use_graph: bool = True) -> dict:
+    """``n_requests`` prompts with lengths uniform in [shortest, longest] (seeded), ``steps`` decode steps, all through
+    ``Engine.generate`` with host token lists in and out: every repetition's prefill and decode times are kept, and
+    summarised by median, 10th and 90th percentile (pico-engine's protocol, src/pico_engine/evidence.py:138-163,
+    294-325, which writes every sample and the environment to its receipt)."""
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(shortest, longest + 1, (n_requests,), generator=g).tolist()
+    vocab = engine.model.plan.vocab_size
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+    engine.max_batch = max(engine.max_batch, n_requests)
+    samples = []
+    with ClockSampler(period_s=0.05) as clocks:
+        for rep in range(warmups + repetitions):
+            t0 = time.perf_counter()
+            out = engine.generate(prompts, max_tokens=steps + 1, temperature=0.0, use_graph=use_graph, stop_token_ids=())
+            wall = time.perf_counter() - t0
+            t = engine.last_timing
+            assert all(len(o) == steps + 1 for o in out)
+            if rep >= warmups:
+                samples.append({"wall_s": wall, "prefill_s": t["prefill_s"], "decode_s": t["decode_s"],
+                                "decode_steps": t["decode_steps"],
+                                "prefill_tokens_per_s": sum(lengths) / t["prefill_s"],
+                                "decode_tokens_per_s": n_requests * t["decode_steps"] / t["decode_s"]})
+    mean_ctx = sum(lengths) / n_requests + steps / 2.0
+    step_bytes = decode_step_bytes(engine, n_requests, mean_ctx)
+    decode = summary([s["decode_tokens_per_s"] for s in samples])
+    return {"requests": n_requests, "prompt_lengths": lengths, "prompt_tokens": sum(lengths), "decode_steps": steps,
+            "graph": use_graph, "samples": samples, "decode_tokens_per_s": decode,
+            "prefill_tokens_per_s": summary([s["prefill_tokens_per_s"] for s in samples]),
+            "decode_bytes_per_step": step_bytes,
+            "decode_gbytes_per_s": step_bytes * decode["median"] / n_requests / 1e9,
+            "clocks": clocks.record(), "weights_bytes": engine.model.step_weight_bytes(),
+            "cache_bytes": engine.cache.bytes() if engine.cache is not None else 0}
+
+
+@torch.inference_mode()
+def last_logits(engine, prompts: Sequence[Sequence[int]], batch: int = 8) -> torch.Tensor:
+    """float32 logits [len(prompts), vocab] at each prompt's last position (prompts run ``batch`` at a time), on the host."""
+    rows = []
+    need = max(sum(sorted(((len(p) + 63) // 64 * 64 for p in prompts), reverse=True)[:batch]), 64)
+    engine.ensure_cache(need, max(len(p) for p in prompts), max_seqs=batch)
+    for at in range(0, len(prompts), batch):
+        group = prompts[at:at + batch]
+        slots = [engine.cache.open() for _ in group]
+        rows.append(engine.stepper.step(slots, group).cpu())
+        for s in slots:
+            engine.cache.close(s)
+    return torch.cat(rows)
+
+
+def agreement(config, seed: int, prompts: Sequence[Sequence[int]]) -> dict:
+    """The bfloat16 engine against the float32 engine on the same weights (drawn once in bfloat16, so that the two
+    differ in arithmetic only): the largest difference of the last-position logits relative to their size, and
+    how often the most likely token is the same."""
+    import gc
+    from .engine.engine import Engine
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_config(config, seed=seed, draw_on="cuda", dtype=dtype)
+        out[dtype] = last_logits(eng, prompts)
+        del eng
+        gc.collect(); torch.cuda.empty_cache()
+    a, b = out["float32"], out["bfloat16"]
+    scale = float(a.abs().max())
+    return {"prompts": len(prompts), "logit_scale": scale, "max_difference_of_scale": float((a - b).abs().max()) / scale,
+            "same_most_likely_token": float((a.argmax(-1) == b.argmax(-1)).float().mean())}
+
+
+def environment() -> dict:
+    """What the numbers were measured on (pico-engine's receipts carry the same, src/pico_engine/evidence.py:294-325)."""
+    import platform
+    p = torch.cuda.get_device_properties(0) if torch.cuda.is_available() else None
+    return {"gpu": p.name if p else None, "sms": p.multi_processor_count if p else None,
+            "memory_gb": round(p.total_memory / 2 ** 30, 1) if p else None, "torch": torch.__version__,
+            "cuda": torch.version.cuda, "python": platform.python_version(), "time": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())}
+
+
 # ---------------------------------------------------------------------------- command line
 
 def main(argv=None) -> None:
@@ -204,6 +337,11 @@ def main(argv=None) -> None:
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
     p.add_argument("--output", help="write the JSON record here")
+    p.add_argument("--requests", type=int, default=0, help="also: generation of this many requests with unequal prompts "
+                   "through Engine.generate (--prompt-lengths, --n-tokens decode steps)")
+    p.add_argument("--prompt-lengths", default="64,2048", metavar="SHORTEST,LONGEST", help="prompt lengths are uniform in this range")
+    p.add_argument("--agreement", action="store_true", help="with --random and --requests: compare the last-position logits of "
+                   "the bfloat16 engine with the float32 engine's on the same weights")
     args = p.parse_args(argv)
     from .engine.engine import Engine
     if (args.model is None) == (args.random is None):
@@ -220,7 +358,10 @@ def main(argv=None) -> None:
     batches = [int(x) for x in args.batch.split(",") if x]
     if batches:
         eng.ensure_cache(max(batches) * ((args.context + 63) // 64) * 64, args.context, max_seqs=max(batches))
-    record = {"model": args.model or args.random, "dtype": args.dtype, "graph": not args.no_graph, "decode": {}, "time": time.time()}
+    record = {"model": args.model or args.random, "dtype": args.dtype, "graph": not args.no_graph, "decode": {},
+              "environment": environment()}
+    if args.random and args.layers:
+        record["layers"] = args.layers
     if args.prefill > 0:
         pre = prefill_device(eng, args.prefill, repetitions=args.repetitions, warmup=args.warmups)
         record["prefill"] = pre
@@ -232,6 +373,28 @@ def main(argv=None) -> None:
         record["decode"][str(b)] = {"tokens_per_s": s, "last": runs[-1]}
         print(f"decode batch {b}: median {s['median']:.0f} tok/s (p10 {s['p10']:.0f}, p90 {s['p90']:.0f}), "
               f"{runs[-1]['gbytes_per_s']:.0f} GB/s of weights and cache, {runs[-1]['launches_per_step']} launches a step")
+    if args.requests > 0:
+        lo, hi = (int(x) for x in args.prompt_lengths.split(","))
+        gen = generate_protocol(eng, args.requests, lo, hi, args.n_tokens, args.warmups, args.repetitions, use_graph=not args.no_graph)
+        record["generate"] = gen
+        d, f = gen["decode_tokens_per_s"], gen["prefill_tokens_per_s"]
+        print(f"generate {args.requests} requests of {lo}..{hi} prompt tokens, {args.n_tokens} steps: decode median {d['median']:.0f} tok/s "
+              f"(p10 {d['p10']:.0f}, p90 {d['p90']:.0f}), {gen['decode_gbytes_per_s']:.0f} GB/s of weights and cache; prefill median "
+              f"{f['median']:.0f} tok/s")
+        if args.agreement:
+            if not args.random:
+                p.error("--agreement needs --random (the float32 engine is drawn from the same seed)")
+            g = torch.Generator().manual_seed(0)
+            lengths = gen["prompt_lengths"]
+            prompts = [torch.randint(0, eng.model.plan.vocab_size, (n,), generator=g).tolist() for n in lengths]
+            config, seed = eng.config, args.seed
+            del eng
+            import gc
+            gc.collect(); torch.cuda.empty_cache()
+            record["agreement"] = agreement(config, seed, prompts)
+            a = record["agreement"]
+            print(f"bfloat16 against float32: logits differ by {a['max_difference_of_scale']:.3g} of their size, "
+                  f"same most likely token in {a['same_most_likely_token']:.2f} of {a['prompts']} prompts")
     if args.output:
         with open(args.output, "w") as f:
             json.dump(record, f, indent=1)

@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
                 const size_t o = (size_t)m * p.N + n;
                 if (EPI == LF_STORE_F32) ((float*)p.out)[o] = v;
                 else if (EPI == LF_STORE_BF16) ((bf16*)p.out)[o] = __float2bfloat16_rn(v);
-                else ((float*)p.out)[o] += v;
+                else atomicAdd((float*)p.out + o, v);     // the only sum into this element: a reduction in memory, no read to wait for
             }
         }
     }

@@ -42,11 +42,19 @@ class Choice:
             b *= 2
         return b
 
+    # A step of many rows is launched kernel by kernel from Python, at 10 to 13 us of host time a launch
+    # (measured: 220 launches of a 2,048-token step of the Qwen2.5-0.5B shape take 3.2 ms), which is as long as
+    # the device needs for them: a launch that the fused kernel saves is worth about this much there.  Steps of up
+    # to CAPTURED_ROWS rows are decode steps, replayed from a graph, where only device time counts.
+    HOST_US_PER_LAUNCH = 6.0
+    CAPTURED_ROWS = 128
+
     @classmethod
-    def pick(cls, key: Tuple, own: Callable[[], object], library: Callable[[], object]) -> str:
+    def pick(cls, key: Tuple, own: Callable[[], object], library: Callable[[], object], launches_saved: int = 0) -> str:
         """"tcgen05" or "library" for ``key``; the two callables run the product on scratch operands
-        of the key's sizes.  While a CUDA graph is being captured nothing can be timed: the library
-        product runs, and the question is asked again outside a capture."""
+        of the key's sizes; ``launches_saved``: how many launches fewer the fused kernel is.  While a CUDA
+        graph is being captured nothing can be timed: the library product runs, and the question is asked
+        again outside a capture."""
         got = cls.table.get(key)
         if got is not None:
             return got
@@ -57,7 +65,8 @@ class Choice:
             return "library"
         t_own, t_lib = _device_time(own), _device_time(library)
         cls.timings[key] = (t_own, t_lib)
-        cls.table[key] = "tcgen05" if t_own < t_lib else "library"
+        host = cls.HOST_US_PER_LAUNCH * launches_saved if key[1] > cls.CAPTURED_ROWS else 0.0
+        cls.table[key] = "tcgen05" if t_own < t_lib + host else "library"
         return cls.table[key]
 
 
@@ -142,7 +151,7 @@ def gate_up_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         if key not in Choice.table:
             sh = _scratch_rows(Choice.bucket(M), h.shape[1], h.dtype, h.device)
             Choice.pick(key, lambda: kernels.gemm_tcgen05(sh, w_gate_up, swiglu=True),
-                        lambda: kernels.swiglu(torch.mm(sh, w_gate_up.t())))
+                        lambda: kernels.swiglu(torch.mm(sh, w_gate_up.t())), launches_saved=1)
         if Choice.table.get(key) == "tcgen05":
             return kernels.gemm_tcgen05(h, w_gate_up, swiglu=True)
     return kernels.swiglu(linear(h, w_gate_up, out_dtype=h.dtype))
@@ -171,7 +180,7 @@ def qkv_rope_store(h: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.T
         def library():
             y = linear(sh, w_qkv, b_qkv, out_dtype=h.dtype)
             kernels.rope_store(y, n_q, n_kv, head_dim, cos, sin, pos, pos, None, None, None, 0)
-        Choice.pick(key, own, library)
+        Choice.pick(key, own, library, launches_saved=1)
     if Choice.table.get(key) != "tcgen05":
         return None
     return kernels.gemm_qkv_rope_store(h, w_qkv, b_qkv, n_q, n_kv, head_dim, cos, sin, tok_pos, tok_row, k_pool, v_pool,
