@@ -200,8 +200,9 @@ def decode_device(engine, batch: int, context: int, steps: int, warmup: int, use
 
 
 @torch.inference_mode()
-def prefill_device(engine, tokens: int, repetitions: int = 5, warmup: int = 3, seed: int = 0) -> dict:
-    """Device time of one step that runs a prompt of ``tokens`` tokens and returns its last logits."""
+def prefill_device(engine, tokens: int, repetitions: int = 5, warmup: int = 3, seed: int = 0, use_graph: bool = True) -> dict:
+    """Device time of one step that runs a prompt of ``tokens`` tokens and returns its last logits: the step as
+    ``Engine.generate`` runs it (with ``use_graph`` a prompt step of sizes that have come before is a captured graph)."""
     engine.ensure_cache(((tokens + 63) // 64) * 64, tokens)
     ids = torch.randint(0, engine.model.plan.vocab_size, (tokens,), generator=torch.Generator().manual_seed(seed)).tolist()
     times = []
@@ -211,7 +212,7 @@ def prefill_device(engine, tokens: int, repetitions: int = 5, warmup: int = 3, s
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         torch.cuda.nvtx.range_push("pico_prefill")
-        engine.stepper.step([s], [ids])
+        engine.stepper.step([s], [ids], use_graph=use_graph)
         torch.cuda.nvtx.range_pop()
         e1.record()
         torch.cuda.synchronize()
@@ -221,7 +222,7 @@ def prefill_device(engine, tokens: int, repetitions: int = 5, warmup: int = 3, s
     ms = percentile(times, 50)
     flops = prefill_flops(engine, tokens)
     return {"tokens": tokens, "ms": ms, "tokens_per_s": tokens * 1000.0 / ms, "flops": flops,
-            "tflops_per_s": flops / ms / 1e9, "times_ms": summary(times)}
+            "tflops_per_s": flops / ms / 1e9, "times_ms": summary(times), "graph": use_graph}
 
 
 def decode_end_to_end(engine, batch: int, context: int, steps: int, use_graph: bool = True, seed: int = 0) -> dict:
@@ -363,7 +364,7 @@ def main(argv=None) -> None:
     if args.random and args.layers:
         record["layers"] = args.layers
     if args.prefill > 0:
-        pre = prefill_device(eng, args.prefill, repetitions=args.repetitions, warmup=args.warmups)
+        pre = prefill_device(eng, args.prefill, repetitions=args.repetitions, warmup=max(args.warmups, 2), use_graph=not args.no_graph)
         record["prefill"] = pre
         print(f"prefill {pre['tokens']} tokens: {pre['ms']:.3f} ms  {pre['tokens_per_s']:.0f} tok/s  {pre['tflops_per_s']:.1f} TFLOP/s")
     for b in batches:

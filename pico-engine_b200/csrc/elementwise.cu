@@ -146,9 +146,72 @@ __global__ void rmsnorm_kernel(float* x, const TY* y, const int* rows_index,
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(xr[i] * rstd * load_as_f(w, w_dtype, i));
 }
 
+// The same for many rows: a warp to a row, eight rows to a block, so that a step of thousands of rows is a few hundred
+// blocks that never wait at a block-wide barrier (the sum of a row's squares is a warp's shuffle).  A lane keeps up
+// to RW_KEEP groups of four elements between the two passes; a longer row is read again (from L2).
+#define RW_KEEP 8
+#define RW_WARPS 8
+
+template <typename TO, typename TY, bool ADD>
+__global__ void __launch_bounds__(32 * RW_WARPS) rmsnorm_rows_kernel(float* x, const TY* y, const void* w, int w_dtype, float eps,
+                                                                     TO* out, int rows, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, r = blockIdx.x * RW_WARPS + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float4* x4 = reinterpret_cast<float4*>(x + (size_t)r * H);
+    TO* o = out + (size_t)r * H;
+    const int n4 = H / 4;
+    float4 v[RW_KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < RW_KEEP; ++k) {
+        const int i = lane + 32 * k;
+        if (i < n4) {
+            v[k] = x4[i];
+            if (ADD) {
+                const float4 a = load4_as_f(y + (size_t)r * H + 4 * i);
+                v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w;
+                x4[i] = v[k];
+            }
+            ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss); ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+        }
+    }
+    for (int i = lane + 32 * RW_KEEP; i < n4; i += 32) {
+        float4 u = x4[i];
+        if (ADD) {
+            const float4 a = load4_as_f(y + (size_t)r * H + 4 * i);
+            u.x += a.x; u.y += a.y; u.z += a.z; u.w += a.w;
+            x4[i] = u;
+        }
+        ss = fmaf(u.x, u.x, ss); ss = fmaf(u.y, u.y, ss); ss = fmaf(u.z, u.z, ss); ss = fmaf(u.w, u.w, ss);
+    }
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < RW_KEEP; ++k) {
+        const int i = lane + 32 * k;
+        if (i < n4) store4(o + 4 * i, v[k].x * rstd * load_as_f(w, w_dtype, 4 * i), v[k].y * rstd * load_as_f(w, w_dtype, 4 * i + 1),
+                           v[k].z * rstd * load_as_f(w, w_dtype, 4 * i + 2), v[k].w * rstd * load_as_f(w, w_dtype, 4 * i + 3));
+    }
+    for (int i = lane + 32 * RW_KEEP; i < n4; i += 32) {
+        const float4 u = x4[i];                               // this lane wrote it, if anyone did
+        store4(o + 4 * i, u.x * rstd * load_as_f(w, w_dtype, 4 * i), u.y * rstd * load_as_f(w, w_dtype, 4 * i + 1),
+               u.z * rstd * load_as_f(w, w_dtype, 4 * i + 2), u.w * rstd * load_as_f(w, w_dtype, 4 * i + 3));
+    }
+}
+
 template <typename TY, bool ADD>
 static int rmsnorm_launch(float* x, const TY* y, const int* rows_index, const void* w, int w_dtype, float eps, void* out,
                           int out_dtype, int rows, int H, cudaStream_t s) {
+    if (!rows_index && rows >= 512 && (H & 3) == 0 && H <= 8192) {      // many whole rows: a warp a row
+        const int blocks = (rows + RW_WARPS - 1) / RW_WARPS;
+        if (out_dtype == PE_F32) PE_TRY(pe_launch(rmsnorm_rows_kernel<float, TY, ADD>, blocks, 32 * RW_WARPS, 0, s, x, y, w, w_dtype, eps, (float*)out, rows, H));
+        else if (out_dtype == PE_BF16) PE_TRY(pe_launch(rmsnorm_rows_kernel<bf16, TY, ADD>, blocks, 32 * RW_WARPS, 0, s, x, y, w, w_dtype, eps, (bf16*)out, rows, H));
+        else return PE_ERR_UNSUPPORTED;
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (out_dtype == PE_F32) PE_TRY(pe_launch(rmsnorm_kernel<float, TY, ADD>, rows, threads, 0, s, x, y, rows_index, w, w_dtype, eps, (float*)out, H));
     else if (out_dtype == PE_BF16) PE_TRY(pe_launch(rmsnorm_kernel<bf16, TY, ADD>, rows, threads, 0, s, x, y, rows_index, w, w_dtype, eps, (bf16*)out, H));

@@ -150,7 +150,7 @@ class EngineBackend:
 
     def prefill(self, slots, prompts, requests) -> List[int]:
         t0 = time.perf_counter()
-        logits = self.e.stepper.step(slots, prompts)
+        logits = self.e.stepper.step(slots, prompts, use_graph=self.use_graph)
         chosen = self.sampler.choose(logits, self._int32(requests), self._int32([0] * len(slots))).tolist()
         self.e.last_timing["prefill_s"] += time.perf_counter() - t0
         return chosen

@@ -16,7 +16,8 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import Cache, pages_for
+from ..cache import PAGE, Cache, pages_for
+from ..ops import kernels
 from ..parts.base import StepContext
 
 
@@ -37,6 +38,7 @@ class StepLayout:
     B: int
     W: int
     widths: List[int]
+    n_tiles: tuple = (0, 0)          # attention runs of at most 64 and of at most 128 tokens (0, 0: every row brings one token)
     ids: int = 0
     pos: int = 0
     row: int = 0
@@ -44,6 +46,7 @@ class StepLayout:
     first: int = 0
     lens: int = 0
     want: int = 0
+    tiles: Optional[List[int]] = None
     tables: Optional[List[int]] = None
     total: int = 0
 
@@ -56,6 +59,9 @@ class StepLayout:
         self.first = o; o += _pad4(self.B + 1)
         self.lens = o; o += _pad4(self.B)
         self.want = o; o += _pad4(max(self.W, 1))
+        self.tiles = []
+        for n in self.n_tiles:
+            self.tiles.append(o); o += 4 * n
         self.tables = []
         for w in self.widths:
             self.tables.append(o); o += _pad4(self.B * w)
@@ -72,6 +78,8 @@ class Stepper:
         self._ring: List[list] = [[None, None] for _ in range(4)]     # pinned staging buffers and their copy events
         self._ring_at = 0
         self.h2d_bytes = 0                        # bytes of step descriptions copied to the device so far
+        self._prompt_graphs: dict = {}            # (rows, tokens) -> GraphedPrompt, the most recently used last
+        self._prompt_pool = None
 
     # ------------------------------------------------------------------ building a step
     def _stage(self, host: np.ndarray):
@@ -88,11 +96,14 @@ class Stepper:
         return slot, slot[0][:n]
 
     def describe(self, slots: Sequence[int], lens: Sequence[int], want: Optional[Sequence[Sequence[int]]],
-                 token_ids: Optional[Sequence[Sequence[int]]], widths: Optional[List[int]] = None):
+                 token_ids: Optional[Sequence[Sequence[int]]], widths: Optional[List[int]] = None,
+                 n_tiles: Optional[tuple] = None):
         """Check the step, reserve its pages and lay its arrays out on the host.
 
         Returns ``(layout, host int32 array, starts)``.  ``want[b]`` are places among row b's
-        tokens of this step; None asks for each row's last token.
+        tokens of this step; None asks for each row's last token.  ``n_tiles``: how many attention runs
+        (of at most 64 and at most 128 tokens) the layout holds, for a step of fixed sizes; where the
+        rows make fewer, the last row's first token is listed again (the same result written twice).
         """
         cache = self.cache
         B = len(slots)
@@ -104,23 +115,41 @@ class Stepper:
         lens = [int(n) for n in lens]
         starts = [cache.length(s) for s in slots]
         for b, n in enumerate(lens):
+            if slots[b] == cache.idle_slot:
+                if not 0 <= n <= PAGE:
+                    raise StepError(f"row {b} is idle and brings {n} tokens; the idle slot holds one page of {PAGE}")
+                continue
             if n < 1:
                 raise StepError(f"row {b} brings no token")
-            if slots[b] == cache.idle_slot and n != 1:
-                raise StepError(f"row {b} is idle and brings {n} tokens; an idle row brings one")
             if starts[b] + n > self.max_context:
                 raise StepError(f"row {b} would reach {starts[b] + n} tokens; the engine was set up for sequences "
                                 f"of at most {self.max_context}")
         if want is None:
-            want = [[n - 1] for n in lens]
+            want = [[n - 1] if n else [] for n in lens]
+            empty_rows = sum(1 for n in lens if n == 0)      # idle rows without a token still have a row of logits: of token 0
+        else:
+            empty_rows = 0
         T = sum(lens)
-        W = sum(len(w) for w in want)
+        W = sum(len(w) for w in want) + empty_rows
         for s, n in zip(live, (n for s, n in zip(slots, lens) if s != cache.idle_slot)):
             cache.reserve(s, n)
         if widths is None:
             widths = [max(pages_for(st + n) for st, n in zip(starts, lens))] * len(cache.groups)
-        lay = StepLayout(T, B, W, widths)
+        tile_rows = ([], [])
+        if any(n != 1 for n in lens):                    # rows that bring several tokens: the runs the attention kernels take
+            tile_rows = tuple(kernels.prefill_tile_rows(lens, starts, t) for t in (kernels.PREFILL_TILE, kernels.PREFILL_TILE_TCGEN05))
+            if n_tiles is not None:
+                b0 = min((b for b in range(B) if lens[b]), key=lambda b: starts[b])       # the row that starts earliest:
+                filler = (b0, sum(lens[:b0]), 1, starts[b0])                                # its first token alone is the cheapest run
+                for rows, n in zip(tile_rows, n_tiles):
+                    if len(rows) > n:
+                        raise StepError(f"the step has {len(rows)} attention runs, its layout holds {n}")
+                    rows.extend([filler] * (n - len(rows)))
+        lay = StepLayout(T, B, W, widths, tuple(len(r) for r in tile_rows))
         host = np.zeros(lay.total, dtype=np.int32)
+        for off, rows in zip(lay.tiles, tile_rows):
+            if rows:
+                host[off: off + 4 * len(rows)] = np.asarray(rows, dtype=np.int32).reshape(-1)
         cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
         for b in range(B):
             a, e = cu[b], cu[b + 1]
@@ -151,7 +180,9 @@ class Stepper:
                 slot_ids: Sequence[int] = ()) -> StepContext:
         tables = {g: dev[off: off + lay.B * lay.widths[g]].view(lay.B, lay.widths[g])
                   for g, off in enumerate(lay.tables)}
-        return StepContext(
+        scratch = {name: dev[off: off + 4 * n].view(n, 4)
+                   for name, off, n in zip(("prefill_tiles", "prefill_tiles_128"), lay.tiles, lay.n_tiles) if n}
+        return StepContext(scratch=scratch,
             T=lay.T, B=lay.B, dtype=self.model.dtype, device=self.device,
             tok_pos=dev[lay.pos: lay.pos + lay.T], tok_row=dev[lay.row: lay.row + lay.T],
             slots=dev[lay.slots: lay.slots + lay.B], row_first=dev[lay.first: lay.first + lay.B + 1],
@@ -171,13 +202,41 @@ class Stepper:
         return dev
 
     # ------------------------------------------------------------------ the step
+    MAX_PROMPT_GRAPHS = 8             # padded prompt steps a stepper keeps (captured ones share one memory pool)
+    MAX_GRAPHED_PROMPT_TOKENS = 16384
+
+    def _prompt_graph(self, n_rows: int, n_tokens: int):
+        """The padded step that takes ``n_rows`` prompts of ``n_tokens`` tokens.  It is captured as a graph once
+        steps of its sizes have come twice (a capture costs two more runs of the step; sizes that never come back
+        are not worth one); until then it runs kernel by kernel, at the same padded sizes and so with the same
+        kernels and results as the replays that follow."""
+        from .graph import GraphedPrompt, prompt_sizes
+        key = prompt_sizes(n_rows, n_tokens)
+        if key[1] > self.MAX_GRAPHED_PROMPT_TOKENS or self.device.type != "cuda":
+            return None
+        g = self._prompt_graphs.pop(key, None)
+        if g is None:
+            if self._prompt_pool is None:
+                self._prompt_pool = torch.cuda.graph_pool_handle()
+            g = GraphedPrompt(self, key[0], key[1], self._prompt_pool)
+            while len(self._prompt_graphs) >= self.MAX_PROMPT_GRAPHS:
+                self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+        self._prompt_graphs[key] = g
+        return g
+
     @torch.inference_mode()
     def step(self, slots: Sequence[int], token_ids: Sequence[Sequence[int]],
              want: Optional[Sequence[Sequence[int]]] = None,
-             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+             device_tokens: Optional[torch.Tensor] = None, use_graph: bool = False) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted places, vocab] on the device, in the
         order of the rows and of ``want``.  With ``device_tokens`` (int32 [B], one token per row,
-        already on the device) ``token_ids`` only gives the rows' lengths (all 1)."""
+        already on the device) ``token_ids`` only gives the rows' lengths (all 1).  ``use_graph``: a step
+        that brings prompts and wants each row's last logits runs at padded sizes (``engine.graph.GraphedPrompt``:
+        rows and tokens filled up with idle rows), from the second time on as a captured graph."""
+        if use_graph and want is None and device_tokens is None and any(len(t) != 1 for t in token_ids):
+            g = self._prompt_graph(len(slots), sum(len(t) for t in token_ids))
+            if g is not None:
+                return g.launch(slots, token_ids)
         if device_tokens is not None:
             lens = [1] * len(slots)
             lay, host, starts = self.describe(slots, lens, want, None)

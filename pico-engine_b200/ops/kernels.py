@@ -316,10 +316,10 @@ PREFILL_TILE_TCGEN05 = 128    # AT_QTILE of csrc/attention_prefill_tcgen05.cu
 TCGEN05_HEAD_DIMS = (64, 128)
 
 
-def prefill_tiles(lens, starts, device, tile: int = PREFILL_TILE) -> torch.Tensor:
-    """int32 [tiles, 4] = (batch row, first packed token, tokens, position of the first token):
-    the packed tokens of a step cut into runs of at most ``tile`` tokens of one sequence, the runs
-    that see the most keys first (they take longest, so they are scheduled first)."""
+def prefill_tile_rows(lens, starts, tile: int = PREFILL_TILE):
+    """[(batch row, first packed token, tokens, position of the first token), ...]: the packed tokens of a
+    step cut into runs of at most ``tile`` tokens of one sequence, the runs that see the most keys first
+    (they take longest, so they are scheduled first)."""
     rows = []
     tok = 0
     for b, (n, st) in enumerate(zip(lens, starts)):
@@ -327,7 +327,12 @@ def prefill_tiles(lens, starts, device, tile: int = PREFILL_TILE) -> torch.Tenso
             rows.append((b, tok + off, min(tile, n - off), st + off))
         tok += n
     rows.sort(key=lambda r: -(r[3] + r[2]))
-    return torch.tensor(rows, dtype=torch.int32).to(device, non_blocking=True)
+    return rows
+
+
+def prefill_tiles(lens, starts, device, tile: int = PREFILL_TILE) -> torch.Tensor:
+    """``prefill_tile_rows`` as int32 [tiles, 4] on ``device``."""
+    return torch.tensor(prefill_tile_rows(lens, starts, tile), dtype=torch.int32).to(device, non_blocking=True)
 
 
 def _prefill_args(q, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, tiles, n_tokens, out):

@@ -314,6 +314,58 @@ def test_many_requests_share_a_few_graphs(models, name, dtype):
         assert second == [plain.generate(cfg, w, p, 6, temperature=0.5, seed=2, request=i) for i, p in enumerate(prompts[:8])]
 
 
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_prompt_steps_as_captured_graphs(models, name, dtype):
+    """With graphs, a step that brings prompts runs as a captured graph of padded sizes from the second time its sizes
+    come up: rows and tokens are filled up with idle rows.  Logits and tokens are those of the step launched kernel by
+    kernel; other prompts of the same sizes, and prompts that continue (pieces), go through the same graph."""
+    eng, cfg, w = models[(name, dtype)]
+    reqs = random_requests(cfg, [33, 5, 70, 1, 100], 50)
+    want = replay.plain_logits(cfg, w, reqs)
+    eng.cache = eng.stepper = None
+    eng.ensure_cache(1024, cfg["max_position_embeddings"], max_seqs=8)
+    st, cache = eng.stepper, eng.cache
+
+    def run(tokens_of, use_graph):
+        slots = [cache.open() for _ in tokens_of]
+        first = st.step(slots, [t[:len(t) // 2 + 1] for t in tokens_of], use_graph=use_graph).cpu()      # a first piece of every prompt
+        for s_ in slots:
+            cache.close(s_)
+        return first
+    prompts = list(reqs.values())
+    eager = run(prompts, False)
+    assert not st._prompt_graphs
+    a = run(prompts, True)                                    # the sizes come up for the first time: padded, kernel by kernel
+    assert next(iter(st._prompt_graphs.values())).graph is None
+    b = run(prompts, True)                                    # captured and replayed
+    c = run(prompts, True)                                    # replayed
+    assert len(st._prompt_graphs) == 1 and next(iter(st._prompt_graphs)) == (10, 128)
+    assert next(iter(st._prompt_graphs.values())).graph is not None
+    assert torch.equal(a, b) and torch.equal(b, c)            # the same kernels at the same sizes, captured or not
+    for got in (a, b, c):
+        assert got.shape == eager.shape
+        for i, (rid, toks) in enumerate(reqs.items()):
+            ok, msg = close_enough(got[i], torch.from_numpy(want[(rid, len(toks) // 2)]), dtype)
+            assert ok, (rid, msg)
+    if dtype == "float32":
+        assert torch.equal(b, eager) and torch.equal(c, eager)
+    # other prompts of other lengths, the same sizes after padding: the same graph, no new capture
+    others = list(random_requests(cfg, [40, 9, 60, 7, 12], 51).values())
+    held = next(iter(st._prompt_graphs.values()))
+    again = run(others, True)
+    assert len(st._prompt_graphs) == 1 and next(iter(st._prompt_graphs.values())) is held
+    ref = run(others, False)
+    ok, msg = close_enough(again, ref, dtype)
+    assert ok, msg
+    cache.check()
+    assert not cache.lengths
+    # through the entry point: three calls with the same prompts give the same tokens, with and without graphs
+    outs = [eng.generate(prompts, max_tokens=5, temperature=0.0, use_graph=g) for g in (True, True, True, False)]
+    assert outs[0] == outs[1] == outs[2]
+    if dtype == "float32":
+        assert outs[2] == outs[3] == [plain.generate(cfg, w, p, 5) for p in prompts]
+
+
 def test_weights_stored_in_float32_stay_so(tmp_path):
     """A checkpoint whose norms and one projection are stored in 32 bits, run by the bfloat16 engine."""
     from pico_engine.engine.engine import Engine
