@@ -211,9 +211,11 @@ def prefill_device(engine, tokens: int, repetitions: int = 5, warmup: int = 3, s
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        torch.cuda.nvtx.range_push("pico_prefill")
+        if i == warmup + repetitions - 1:                 # one step, the last, is marked for a profiler's launch list
+            torch.cuda.nvtx.range_push("pico_prefill")
         engine.stepper.step([s], [ids], use_graph=use_graph)
-        torch.cuda.nvtx.range_pop()
+        if i == warmup + repetitions - 1:
+            torch.cuda.nvtx.range_pop()
         e1.record()
         torch.cuda.synchronize()
         engine.cache.close(s)
@@ -312,6 +314,46 @@ def agreement(config, seed: int, prompts: Sequence[Sequence[int]]) -> dict:
             "same_most_likely_token": float((a.argmax(-1) == b.argmax(-1)).float().mean())}
 
 
+@torch.inference_mode()
+def product_times(engine, rows: int) -> dict:
+    """Device time of the first layer's four matrix products at ``rows`` rows, each as this library's tcgen05 kernel
+    with its fused epilogue and as the library product followed by this library's separate kernel: the measurement
+    by which ``ops.linear`` chooses (a captured graph of six calls, best of three replays), in microseconds."""
+    import sys
+    from .ops import kernels
+    L = sys.modules[__package__ + ".ops.linear"]
+    layer = engine.model.layers[0]
+    att, ffn = layer.mixer, layer.feed_forward
+    dev, dt = engine.device, torch.bfloat16
+    out = {}
+    if engine.dtype != dt or att is None or ffn is None or not hasattr(att, "w_qkv") or not hasattr(ffn, "w_gate_up"):
+        return out
+    s = att.spec
+    h = torch.randn(rows, s.hidden, device=dev).to(dt)
+    a = torch.randn(rows, att.w_o.shape[1], device=dev).to(dt)
+    act = torch.randn(rows, ffn.w_down.shape[1], device=dev).to(dt)
+    x = torch.zeros(rows, s.hidden, device=dev)
+    pos = torch.zeros(rows, dtype=torch.int32, device=dev)
+    engine.model.prepare(max(rows, 64))
+    cos, sin = getattr(att.position, "cos", None), getattr(att.position, "sin", None)
+    t = L._device_time
+    out["gate_up_swiglu"] = {"tcgen05": t(lambda: kernels.gemm_tcgen05(h, ffn.w_gate_up, swiglu=True)),
+                             "library": t(lambda: kernels.swiglu(torch.mm(h, ffn.w_gate_up.t())))}
+    if s.head_dim in kernels.GEMM_ROPE_HEAD_DIMS:
+        def library_qkv():
+            y = torch.addmm(att.b_qkv, h, att.w_qkv.t()) if att.b_qkv is not None else torch.mm(h, att.w_qkv.t())
+            kernels.rope_store(y, s.n_heads, s.n_kv_heads, s.head_dim, cos, sin, pos, pos, None, None, None, 0)
+        out["qkv_rope"] = {"tcgen05": t(lambda: kernels.gemm_qkv_rope_store(h, att.w_qkv, att.b_qkv, s.n_heads, s.n_kv_heads,
+                                                                              s.head_dim, cos, sin, pos, pos, None, None, None, 0)),
+                           "library": t(library_qkv)}
+    out["o_proj_residual"] = {"tcgen05": t(lambda: kernels.gemm_tcgen05(a, att.w_o, accumulate_into=x)),
+                              "library": t(lambda: kernels.residual_add(x, torch.mm(a, att.w_o.t())))}
+    out["down_residual"] = {"tcgen05": t(lambda: kernels.gemm_tcgen05(act, ffn.w_down, accumulate_into=x)),
+                            "library": t(lambda: kernels.residual_add(x, torch.mm(act, ffn.w_down.t())))}
+    kernels.check_status(dev)
+    return out
+
+
 def environment() -> dict:
     """What the numbers were measured on (pico-engine's receipts carry the same, src/pico_engine/evidence.py:294-325)."""
     import platform
@@ -338,6 +380,10 @@ def main(argv=None) -> None:
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
     p.add_argument("--output", help="write the JSON record here")
+    p.add_argument("--save-choices", metavar="FILE", help="write which implementation each matrix product got (ops.linear.Choice); "
+                   "PICO_ENGINE_GEMM_CHOICES=FILE makes a later run start from them")
+    p.add_argument("--products", default="", metavar="ROWS[,ROWS...]", help="also: the first layer's matrix products at these "
+                   "row counts, as this library's fused tcgen05 kernel and as the library product plus the separate pass")
     p.add_argument("--requests", type=int, default=0, help="also: generation of this many requests with unequal prompts "
                    "through Engine.generate (--prompt-lengths, --n-tokens decode steps)")
     p.add_argument("--prompt-lengths", default="64,2048", metavar="SHORTEST,LONGEST", help="prompt lengths are uniform in this range")
@@ -374,6 +420,11 @@ def main(argv=None) -> None:
         record["decode"][str(b)] = {"tokens_per_s": s, "last": runs[-1]}
         print(f"decode batch {b}: median {s['median']:.0f} tok/s (p10 {s['p10']:.0f}, p90 {s['p90']:.0f}), "
               f"{runs[-1]['gbytes_per_s']:.0f} GB/s of weights and cache, {runs[-1]['launches_per_step']} launches a step")
+    for rows in [int(x) for x in args.products.split(",") if x]:
+        times = product_times(eng, rows)
+        record.setdefault("products", {})[str(rows)] = times
+        for name, t in times.items():
+            print(f"{rows} rows {name}: tcgen05 {t['tcgen05']:.1f} us, library {t['library']:.1f} us")
     if args.requests > 0:
         lo, hi = (int(x) for x in args.prompt_lengths.split(","))
         gen = generate_protocol(eng, args.requests, lo, hi, args.n_tokens, args.warmups, args.repetitions, use_graph=not args.no_graph)
@@ -396,6 +447,13 @@ def main(argv=None) -> None:
             a = record["agreement"]
             print(f"bfloat16 against float32: logits differ by {a['max_difference_of_scale']:.3g} of their size, "
                   f"same most likely token in {a['same_most_likely_token']:.2f} of {a['prompts']} prompts")
+    import sys
+    choice = sys.modules[__package__ + ".ops.linear"].Choice
+    record["product_choices"] = {"|".join(str(x) for x in k): {"taken": v, "tcgen05_us": choice.timings.get(k, (None, None))[0],
+                                                               "library_us": choice.timings.get(k, (None, None))[1]}
+                                 for k, v in choice.table.items()}
+    if args.save_choices:
+        choice.save(args.save_choices)
     if args.output:
         with open(args.output, "w") as f:
             json.dump(record, f, indent=1)

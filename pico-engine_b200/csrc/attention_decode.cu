@@ -529,7 +529,7 @@ struct AdVariant {
 
     static int launch(dim3 grid, int n_splits, int stages, cudaStream_t stream, const bf16* q, int q_stride, const bf16* k_pool,
                       const bf16* v_pool, const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
-                      int nh, int nkv, int window, float scale_log2e, int* status, bf16* out) {
+                      int nh, int nkv, int window, float scale_log2e, int* status, bf16* out, bool early) {
         const size_t smem = smem_bytes(stages);
         { const int e = allow_smem(smem); if (e) return e; }
         cudaLaunchConfig_t cfg = {};
@@ -539,7 +539,7 @@ struct AdVariant {
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         int n_attr = 0;
-        if (pe_pdl_enabled()) {
+        if (pe_pdl_enabled() && early) {                   // without it the kernel starts when all work before it in the stream has ended
             attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
             ++n_attr;
@@ -591,7 +591,10 @@ extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_contex
 extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                    const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
                                    int T, int nh, int nkv, int hd, int window, float scale, int max_context,
-                                   int* status, void* stream) {
+                                   int early_pages, int* status, void* stream) {
+    // early_pages 1: the kernel may start while the kernels before it in the stream still run, and copies cache pages
+    // at once; those kernels (the one before it, and the one before that, which it can overlap too) must then have
+    // written no cache row but each token's own (which is fetched again after the wait).  0: it starts when they have ended.
     if (T <= 0) return 0;
     if (hd != AD_HD || nkv <= 0 || nh % nkv || max_context <= 0 || q_stride % 8 || T > 65535 || !status) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) return PE_ERR_UNSUPPORTED;
@@ -606,9 +609,9 @@ extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const
         if (wide)
             return AdVariant<16>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
                                          (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window,
-                                         scale_log2e, status, (bf16*)out);
+                                         scale_log2e, status, (bf16*)out, early_pages != 0);
     }
     return AdVariant<8>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
                                 (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window, scale_log2e,
-                                status, (bf16*)out);
+                                status, (bf16*)out, early_pages != 0);
 }

@@ -204,7 +204,9 @@ __global__ void __launch_bounds__(32 * RW_WARPS) rmsnorm_rows_kernel(float* x, c
 template <typename TY, bool ADD>
 static int rmsnorm_launch(float* x, const TY* y, const int* rows_index, const void* w, int w_dtype, float eps, void* out,
                           int out_dtype, int rows, int H, cudaStream_t s) {
-    if (!rows_index && rows >= 512 && (H & 3) == 0 && H <= 8192) {      // many whole rows: a warp a row
+    // many whole rows: a warp a row.  Measured inside a graph at 896 columns: level with a block a row at 2,048 rows
+    // (3.7 against 4.2 us, with the residual sum 6.0 against 5.3 us), ahead at 8,192 (10.0 against 12.6, 17.5 against 19.2 us)
+    if (!rows_index && rows >= 4096 && (H & 3) == 0 && H <= 8192) {
         const int blocks = (rows + RW_WARPS - 1) / RW_WARPS;
         if (out_dtype == PE_F32) PE_TRY(pe_launch(rmsnorm_rows_kernel<float, TY, ADD>, blocks, 32 * RW_WARPS, 0, s, x, y, w, w_dtype, eps, (float*)out, rows, H));
         else if (out_dtype == PE_BF16) PE_TRY(pe_launch(rmsnorm_rows_kernel<bf16, TY, ADD>, blocks, 32 * RW_WARPS, 0, s, x, y, w, w_dtype, eps, (bf16*)out, rows, H));

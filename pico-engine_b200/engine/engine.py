@@ -19,7 +19,7 @@ from ..ops import kernels
 from ..ops.library import core, require_cuda
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_folder, load_into, random_tensor
-from .generate import Request, generate as run_generation, held_tokens
+from .generate import Request, cut_prompts, generate as run_generation, held_tokens
 from .graph import GraphedDecode, TokenLoop, bucket_rows
 from .step import Stepper
 
@@ -38,7 +38,8 @@ class Engine:
     """A loaded model with its cache, step function and generation loop on one CUDA device.
 
     ``max_tokens_in_cache``: the most tokens live sequences hold at any time, each rounded up to a
-    page of 64; ``max_context``: the longest single sequence; ``max_batch``: sequences per batch.
+    page of 64; ``max_context``: the longest single sequence; ``max_batch``: sequences per batch;
+    ``prefill_tokens_per_step`` (an attribute, 16,384): the most prompt tokens one step takes.
     The cache is allocated on first use and grows when a call needs more.
     """
 
@@ -62,6 +63,7 @@ class Engine:
             load_into(self.model, lambda n: random_tensor(n, expected[n], _seed, store, _draw_on),
                       {n: s.shape for n, s in expected.items()}, "the random weights")
         self.max_batch = max_batch
+        self.prefill_tokens_per_step = 16384      # prompts of a batch beyond this many tokens are run in several steps
         self._want_tokens = max_tokens_in_cache
         self._want_context = max_context
         self.cache: Optional[Cache] = None
@@ -149,8 +151,23 @@ class EngineBackend:
         return torch.tensor(list(values), dtype=torch.int32).to(self.e.device, non_blocking=True)
 
     def prefill(self, slots, prompts, requests) -> List[int]:
+        """The prompts of a batch: in one step, or, where they have more tokens than ``Engine.prefill_tokens_per_step``,
+        in several (the activations of a step grow with its tokens: the cache may hold a batch whose prompts in one
+        step would not fit beside it).  A prompt's later pieces start inside its sequence; the logits that choose a
+        request's first token are those of its last piece's last token."""
         t0 = time.perf_counter()
-        logits = self.e.stepper.step(slots, prompts, use_graph=self.use_graph)
+        budget = self.e.prefill_tokens_per_step
+        if sum(len(p) for p in prompts) <= budget:
+            logits = self.e.stepper.step(slots, prompts, use_graph=self.use_graph)
+        else:
+            rows = [None] * len(slots)
+            for pieces in cut_prompts([len(p) for p in prompts], budget):
+                ends = [at + n == len(prompts[r]) for r, at, n in pieces]
+                out = self.e.stepper.step([slots[r] for r, _, _ in pieces], [prompts[r][at:at + n] for r, at, n in pieces],
+                                          [[n - 1] if end else [] for (_, _, n), end in zip(pieces, ends)])
+                for k, r in enumerate(r for (r, _, _), end in zip(pieces, ends) if end):
+                    rows[r] = out[k]
+            logits = torch.stack(rows)
         chosen = self.sampler.choose(logits, self._int32(requests), self._int32([0] * len(slots))).tolist()
         self.e.last_timing["prefill_s"] += time.perf_counter() - t0
         return chosen

@@ -71,6 +71,29 @@ def plan_batches(requests: Sequence[Request], max_batch: int, max_tokens: int) -
     return batches
 
 
+def cut_prompts(lengths: Sequence[int], tokens_per_step: int) -> List[List[tuple]]:
+    """The prompts of a batch cut into steps of at most ``tokens_per_step`` tokens: ``[[(row, first token, tokens), ...],
+    ...]``.  Rows are taken in order; a prompt that does not fit what is left of a step goes on in the next one, so
+    every row's pieces come in consecutive steps and its last piece ends in the step whose logits choose its first
+    token.  A batch that fits one step is one step."""
+    if tokens_per_step < 1:
+        raise GenerationError("a step must take at least one token")
+    steps, cur, room = [], [], tokens_per_step
+    for row, n in enumerate(lengths):
+        at = 0
+        while at < n:
+            if room == 0:
+                steps.append(cur)
+                cur, room = [], tokens_per_step
+            take = min(n - at, room)
+            cur.append((row, at, take))
+            at += take
+            room -= take
+    if cur:
+        steps.append(cur)
+    return steps
+
+
 def _settle(rows: Sequence[Request], chosen: Sequence[int], stop: frozenset) -> None:
     """Give every row of a step its chosen token: a stop token ends the request (and is neither
     returned nor fed back), the token that fills ``max_new_tokens`` ends it too.  Rows of

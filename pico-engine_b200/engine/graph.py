@@ -14,6 +14,7 @@ eager fallback with a warning if capture fails.
 """
 from __future__ import annotations
 
+import gc
 import warnings
 from typing import List, Optional, Sequence
 
@@ -57,6 +58,20 @@ class TokenLoop:
         self._pinned[i][:B].copy_(self.chosen[:B], non_blocking=True)
         self._events[i].record()
         return InFlight(B, self._pinned[i], self._events[i])
+
+
+class _collector_paused:
+    """While a capture records, Python's cycle collector stays off: were it to free an object that owns a captured graph
+    or other device resources in the middle of the capture, the release would be a forbidden operation on a capturing
+    stream and break the capture.  (torch's capture context collects once before it starts.)"""
+
+    def __enter__(self):
+        self.was_on = gc.isenabled()
+        gc.disable()
+
+    def __exit__(self, *exc):
+        if self.was_on:
+            gc.enable()
 
 
 def _leave_failed_capture(stream) -> None:
@@ -142,7 +157,7 @@ class GraphedPrompt:
                     cache.restore_state(state)
                 torch.cuda.current_stream().wait_stream(side)
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, pool=self.pool):
+                with _collector_paused(), torch.cuda.graph(graph, pool=self.pool):
                     self._forward(ctx)
                 self.graph = graph
             except Exception as e:                        # noqa: BLE001 - any capture failure means launching kernel by kernel
@@ -246,7 +261,7 @@ class GraphedDecode:
         torch.cuda.current_stream().wait_stream(side)
         self.loop.chosen.copy_(keep)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with _collector_paused(), torch.cuda.graph(graph):
             self._forward()
         self.loop.chosen.copy_(keep)
         self.graph = graph

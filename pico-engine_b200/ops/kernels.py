@@ -288,11 +288,12 @@ def linear_mma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
 def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                      tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
-                     max_context: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     max_context: int, out: Optional[torch.Tensor] = None, early_pages: bool = True) -> torch.Tensor:
     """Attention of T single tokens (bfloat16) over the cache; ``max_context`` bounds every
-    token's position + 1 and fixes the launch shape.  The kernel before this one on the stream may
-    have written keys and values at each token's own position only: older pages are read while
-    that kernel still runs."""
+    token's position + 1 and fixes the launch shape.  With ``early_pages`` the kernel copies cache pages
+    while the two kernels before it on the stream may still run: they must have written keys and values
+    at each token's own position only (the library's own parts do).  A part that rewrites other cache
+    rows shortly before attending passes False: the kernel then starts when everything before it has ended."""
     from .library import for_head_dim
     T = tok_pos.shape[0]
     _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
@@ -307,7 +308,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
     check(lib.pe_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
                                   n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context),
-                                  status_ptr(q.device), stream_ptr()), "attention_decode")
+                                  1 if early_pages else 0, status_ptr(q.device), stream_ptr()), "attention_decode")
     return out
 
 
@@ -382,14 +383,16 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, n_heads: int, n_kv
 
 def attention(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int, k_pool: torch.Tensor,
               v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int, tok_pos: torch.Tensor,
-              tok_row: torch.Tensor, window: Optional[int], scale: float, ctx) -> torch.Tensor:
+              tok_row: torch.Tensor, window: Optional[int], scale: float, ctx, own_rows_only: bool = True) -> torch.Tensor:
     """Attention of the step's tokens over the cache, with the kernel the step calls for:
     bfloat16 uses the tensor-core kernels (single tokens: decode; longer runs: prefill),
-    float32 the float32 kernel."""
+    float32 the float32 kernel.  ``own_rows_only``: the kernels launched just before wrote no cache row
+    but each token's own (see ``attention_decode``); a caller that cannot promise this passes False."""
     if q.dtype == torch.bfloat16:
         if ctx.one_token_each:
             return attention_decode(q, q_stride, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table,
-                                    table_stride, tok_pos, tok_row, window, scale, ctx.max_context)
+                                    table_stride, tok_pos, tok_row, window, scale, ctx.max_context,
+                                    early_pages=own_rows_only)
         tcgen05 = attention_prefill_tcgen05_takes(head_dim, scale)
         name = "prefill_tiles_128" if tcgen05 else "prefill_tiles"
         tiles = ctx.scratch.get(name)

@@ -38,7 +38,7 @@ _SIGNATURES = {
 }
 
 _HEAD_DIM_SIGNATURES = {
-    "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, P, P],
+    "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P, P],
     "pe_attention_decode_splits": [I, I, I, I, P],
     "pe_attention_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
     "pe_attention_prefill_tcgen05": [P, I, P, P, P, LL, P, I, P, I, I, I, I, I, I, F, P, P],

@@ -17,6 +17,7 @@ follows it in a layer: the choice of kernel for a matrix product.
 """
 from __future__ import annotations
 
+import gc
 import os
 from typing import Callable, Dict, Optional, Tuple
 
@@ -25,6 +26,7 @@ import torch
 from . import kernels
 
 _FORCED = os.environ.get("PICO_ENGINE_GEMM", "auto").lower()      # auto | tcgen05 | library
+_CHOICES_FILE = os.environ.get("PICO_ENGINE_GEMM_CHOICES")        # a JSON file of earlier decisions (Choice.save) to start from
 
 
 class Choice:
@@ -33,6 +35,25 @@ class Choice:
 
     table: Dict[Tuple, str] = {}
     timings: Dict[Tuple, Tuple[float, float]] = {}       # key -> (tcgen05 us, library us), for reports
+
+    @classmethod
+    def save(cls, path: str) -> None:
+        """Write the decisions made so far; ``PICO_ENGINE_GEMM_CHOICES=path`` makes a later process start from them
+        (no timing for shapes that are listed: a run under a profiler, whose clock is not the device's, keeps the
+        choices of a plain run; a service skips the first-use measurements)."""
+        import json
+        with open(path, "w") as f:
+            json.dump({"|".join(str(x) for x in k): v for k, v in cls.table.items()}, f, indent=1, sort_keys=True)
+
+    @classmethod
+    def load(cls, path: str) -> None:
+        import json
+        with open(path) as f:
+            for k, v in json.load(f).items():
+                if v not in ("tcgen05", "library"):
+                    raise ValueError(f"{path}: the choice for {k} must be tcgen05 or library, not {v!r}")
+                parts = k.split("|")
+                cls.table[(parts[0],) + tuple(int(x) for x in parts[1:])] = v
 
     @staticmethod
     def bucket(rows: int) -> int:
@@ -70,6 +91,10 @@ class Choice:
         return cls.table[key]
 
 
+if _CHOICES_FILE and os.path.isfile(_CHOICES_FILE):
+    Choice.load(_CHOICES_FILE)
+
+
 def _device_time(fn: Callable[[], object], calls: int = 6, replays: int = 3) -> float:
     """Microseconds a call of ``fn`` takes on the device: ``calls`` of them in one captured graph (no host
     in between), the best of ``replays`` replays."""
@@ -78,11 +103,17 @@ def _device_time(fn: Callable[[], object], calls: int = 6, replays: int = 3) -> 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        fn()
-        with torch.cuda.graph(graph, stream=side):
-            for _ in range(calls):
-                fn()
+    collecting = gc.isenabled()
+    gc.disable()                                 # nothing that owns device resources is freed in the middle of a capture
+    try:
+        with torch.cuda.stream(side):
+            fn()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(calls):
+                    fn()
+    finally:
+        if collecting:
+            gc.enable()
     torch.cuda.current_stream().wait_stream(side)
     graph.replay()
     torch.cuda.synchronize()

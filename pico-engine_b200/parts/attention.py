@@ -79,11 +79,11 @@ class GQAAttention(Mixer):
                                ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None, kv.table, kv.stride)
             if q is not None:
                 return kernels.attention(q, q.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table,
-                                         kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
+                                         kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx, own_rows_only=owns_cache)
         qkv = linear(h, self.w_qkv, self.b_qkv, out_dtype=ctx.dtype)
         self.position.rotate_and_store(qkv, s.n_heads, s.n_kv_heads, s.head_dim, ctx, kv if owns_cache else None)
         return kernels.attention(qkv, qkv.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table,
-                                 kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
+                                 kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx, own_rows_only=owns_cache)
 
     def _tables(self, ctx):
         """The rotary tables of this layer's position encoding (None, None where it has none), checked
@@ -117,8 +117,9 @@ class GQAAttention(Mixer):
             q = kernels.norm_qkv_rope_store(x, norm.weight, norm.eps, self.w_qkv, self.b_qkv, s.n_heads, s.n_kv_heads,
                                             s.head_dim, cos, sin, ctx.tok_pos, ctx.tok_row,
                                             kv.k if owns_cache else None, kv.v if owns_cache else None, kv.table, kv.stride)
+            # (an entry that reads another entry's cache may follow it closely: that entry's kernels wrote its rows)
             a = kernels.attention(q, q.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table, kv.stride,
-                                  ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx)
+                                  ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx, own_rows_only=owns_cache)
             kernels.linear_fused(a, self.w_o, accumulate_into=x)
             return
         a = self._attend(ctx.normed(x, norm), ctx, cache_entry, owns_cache)

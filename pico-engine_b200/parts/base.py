@@ -5,6 +5,12 @@ No part knows which model it is in: it gets its sizes and constants from its spe
 tensors by the names in its spec, and everything about the running step from the
 :class:`StepContext`.
 
+A rule for parts that write the key/value cache: the decode attention kernel (``kernels.attention`` for single
+tokens in bfloat16) starts copying cache pages while the two kernels launched before it may still run, and
+fetches again only each token's own newest row.  A part that writes other rows of a cache shortly before that
+cache is attended to (within two launches) passes ``own_rows_only=False`` to ``kernels.attention``; the
+attention part does so for a schedule entry that reads another entry's cache (``cache_of``).
+
 Interfaces
 ----------
 Norm          ``forward(x_f32 [T,H], out_dtype, rows_index=None) -> [rows,H]``; optionally

@@ -8,12 +8,29 @@ from ..ops import kernels
 from .base import Position, register_position
 
 
+_TABLES = {}      # (head_dim, theta, device) -> (cos, sin) for the most positions asked for so far
+
+
+def rotary_tables(head_dim: int, theta: float, max_positions: int, device):
+    """cos and sin [positions >= max_positions, head_dim / 2] float32 on ``device``, one pair per (head size, base,
+    device) for all layers and engines of the process: the layers of a model have the same tables, and a decode
+    step that reads the same few rows in every layer finds them in cache."""
+    key = (head_dim, float(theta), str(device))
+    have = _TABLES.get(key)
+    if have is None or have[0].shape[0] < max_positions:
+        inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+        angles = torch.arange(max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        have = _TABLES[key] = (angles.cos().to(device).contiguous(), angles.sin().to(device).contiguous())
+    return have
+
+
 @register_position(RotaryHalfSpec)
 class RotaryHalf(Position):
     """Rotate-half rotary encoding (pico-engine src/pico_engine/model.py:75-79, kernels.py:37-47).
 
     The cos/sin tables are computed once, in float32 on the host with the project's own
     formula, for as many positions as a sequence can have; the kernel reads them by position.
+    All layers with the same head size and base share one pair of tables (``rotary_tables``).
     """
 
     def __init__(self, spec: RotaryHalfSpec, dtype, device):
@@ -21,11 +38,7 @@ class RotaryHalf(Position):
         self.cos = self.sin = None
 
     def prepare(self, max_positions: int) -> None:
-        hd = self.spec.head_dim
-        inv_freq = 1.0 / (self.spec.theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
-        angles = torch.arange(max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
-        self.cos = angles.cos().to(self.device).contiguous()
-        self.sin = angles.sin().to(self.device).contiguous()
+        self.cos, self.sin = rotary_tables(self.spec.head_dim, self.spec.theta, max_positions, self.device)
 
     def weights(self):
         return []                      # the tables are read by position, a few rows a step

@@ -88,3 +88,20 @@ def test_schedule_validation():
     for bad in ((ScheduleEntry(5),), (ScheduleEntry(0, cache_of=0),), (ScheduleEntry(0), ScheduleEntry(1, cache_of=0), ScheduleEntry(0, cache_of=1))):
         with pytest.raises(ConfigError):
             replace(plan, schedule=bad).validate()
+
+
+def test_layers_share_their_rotary_tables():
+    """One pair of cos/sin tables per (head size, base, device), grown when a longer one is asked for."""
+    import torch
+    from pico_engine.config.specs import RotaryHalfSpec
+    from pico_engine.parts.position import RotaryHalf, rotary_tables
+    a, b, c = (RotaryHalf(RotaryHalfSpec(hd, th), torch.float32, "cpu") for hd, th in ((16, 1e4), (16, 1e4), (16, 1e6)))
+    for part in (a, b, c):
+        part.prepare(100)
+    assert a.cos.data_ptr() == b.cos.data_ptr() and a.cos.data_ptr() != c.cos.data_ptr() and a.cos.shape == (100, 8)
+    longer = rotary_tables(16, 1e4, 300, "cpu")[0]
+    assert longer.shape[0] == 300 and torch.equal(longer[:100], a.cos)
+    b.prepare(200)
+    assert b.cos.data_ptr() == longer.data_ptr()                # what is there already is long enough
+    inv = 1.0 / (1e4 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
+    assert torch.allclose(a.sin[7], torch.sin(7 * inv))

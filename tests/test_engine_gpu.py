@@ -366,6 +366,32 @@ def test_prompt_steps_as_captured_graphs(models, name, dtype):
         assert outs[2] == outs[3] == [plain.generate(cfg, w, p, 5) for p in prompts]
 
 
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("budget", [64, 33])
+def test_generation_with_prompts_in_portions(models, name, dtype, budget):
+    """A batch whose prompts have more tokens than a step may take is prefilled in several steps: with 64 tokens a step
+    the cuts fall on page edges and leave the first prompt (66 or 130 tokens) a tail of two; with 33 they fall inside pages and, for
+    B, one token past its window of 32.  The tokens are those of prompts taken whole."""
+    eng, cfg, w = models[(name, dtype)]
+    prompts = list(random_requests(cfg, [66 if name == "A" else 130, 64, 7, 100, 65], 60 + budget).values())
+    whole = eng.generate(prompts, max_tokens=6, temperature=0.0, use_graph=False)
+    eng.prefill_tokens_per_step, old = budget, eng.prefill_tokens_per_step
+    try:
+        cut = eng.generate(prompts, max_tokens=6, temperature=0.0, use_graph=False)
+        cut_graphed = eng.generate(prompts, max_tokens=6, temperature=0.0, use_graph=True)
+    finally:
+        eng.prefill_tokens_per_step = old
+    assert not eng.cache.lengths
+    if dtype == "float32":
+        assert cut == whole == cut_graphed == [plain.generate(cfg, w, p, 6) for p in prompts]
+    else:
+        for p, out in zip(prompts, cut):
+            logits = plain.forward(cfg, w, p + out)
+            for i, tok in enumerate(out):
+                row = logits[len(p) + i - 1]
+                assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max())), (i, tok)
+
+
 def test_weights_stored_in_float32_stay_so(tmp_path):
     """A checkpoint whose norms and one projection are stored in 32 bits, run by the bfloat16 engine."""
     from pico_engine.engine.engine import Engine

@@ -177,3 +177,23 @@ def test_one_step_ahead_batches_and_failures():
     with pytest.raises(RuntimeError, match="device lost"):
         generate(be, [[1], [2]], 8, stop_token_ids=[], max_batch=2, max_tokens=4096)
     assert not be.open_slots and not be.begun                               # nothing stays held or in flight
+
+
+def test_prompts_are_cut_into_steps_of_a_token_budget():
+    from pico_engine.engine.generate import GenerationError, cut_prompts
+    assert cut_prompts([5, 9, 13], 100) == [[(0, 0, 5), (1, 0, 9), (2, 0, 13)]]
+    steps = cut_prompts([5, 9, 13], 8)
+    assert steps == [[(0, 0, 5), (1, 0, 3)], [(1, 3, 6), (2, 0, 2)], [(2, 2, 8)], [(2, 10, 3)]]
+    for lengths, budget in (([70, 1, 64, 200], 64), ([3], 1), ([128, 128], 128), ([1, 1, 1], 2)):
+        steps = cut_prompts(lengths, budget)
+        assert all(0 < sum(n for _, _, n in st) <= budget for st in steps)
+        assert all(sum(n for _, _, n in st) == budget for st in steps[:-1])          # every step but the last is full
+        seen = {}
+        for k, st in enumerate(steps):
+            assert len({r for r, _, _ in st}) == len(st)                                # a row comes once in a step
+            for r, at, n in st:
+                assert at == seen.get(r, (0, k))[0] and k - seen.get(r, (0, k))[1] <= 1 # pieces follow on, in consecutive steps
+                seen[r] = (at + n, k)
+        assert [seen[r][0] for r in range(len(lengths))] == lengths
+    with pytest.raises(GenerationError):
+        cut_prompts([3], 0)

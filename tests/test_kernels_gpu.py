@@ -71,9 +71,10 @@ def test_add_rmsnorm(K, H, ydtype):
 
 
 @pytest.mark.parametrize("H", [100, 896, 1024, 1028])
-def test_rmsnorm_of_many_rows(K, H):
-    """More rows than the device holds blocks at once."""
-    x, y, w = rnd(2601, H, seed=1, scale=3.0), bf(rnd(2601, H, seed=4)), bf(1 + rnd(H, seed=2) * 0.1)
+@pytest.mark.parametrize("rows", [2601, 4100])
+def test_rmsnorm_of_many_rows(K, H, rows):
+    """More rows than the device holds blocks at once; from 4,096 rows on a warp takes a row."""
+    x, y, w = rnd(rows, H, seed=1, scale=3.0), bf(rnd(rows, H, seed=4)), bf(1 + rnd(H, seed=2) * 0.1)
     for odtype, tol in (("f32", 1e-5), ("bf16", 2e-2)):
         got = K.rmsnorm(dev(x), dev(w), 1e-6, DT[odtype])
         assert torch.allclose(got.float().cpu(), plain.rms_norm(x, w, 1e-6), atol=tol, rtol=tol)
@@ -231,6 +232,11 @@ def test_attention_decode(K, nh, nkv, hd, lens, window, max_context):
                           one_query_attention(q, paged, tok_row, tok_pos, nh, window).reshape(len(tok_row), -1), atol=1e-5)
     err = attention_error(got, one_query_attention(q, paged, tok_row, tok_pos, nh, window), "decode")
     assert err < ATTENTION_BOUND, err
+    # started only when everything before it has ended (for callers that rewrite other cache rows): the same numbers
+    late = K.attention_decode(dev(buf.to(torch.bfloat16)), stride, nh, nkv, hd, kp, vp, table, table.shape[1],
+                              dev(torch.tensor(tok_pos, dtype=torch.int32)), dev(torch.tensor(tok_row, dtype=torch.int32)),
+                              window, hd ** -0.5, max_context or max(lens), early_pages=False)
+    assert torch.equal(late, got)
 
 
 def one_query_attention(q_rows, paged, tok_row, tok_pos, nh, window):
