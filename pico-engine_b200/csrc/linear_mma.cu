@@ -1,3 +1,8 @@
+// NOT ON THE GENERATION PATH: no step of the engine calls this kernel any more (up to 16 rows run linear_fused.cu,
+// more rows gemm_tcgen05.cu or the library's product).  It is kept for the entry point that allocates nothing
+// (pe_linear_mma_static at the end of this file, declared in linear_mma_static.h) and for the tests of both:
+// tuning it speeds nothing up.
+//
 // out[M, N] = A[M, K] . W[N, K]^T (+ bias) for few rows M (decoding: one row per sequence),
 // bfloat16 operands, float32 accumulation on the tensor cores (mma.sync m16n8k16).
 //
