@@ -102,7 +102,8 @@ def kv_bytes_per_token(engine) -> int:
     itemsize = torch.empty(0, dtype=engine.dtype).element_size()
     for need in engine.model.cache_needs():
         if need is not None and need.kv is not None:
-            total += 2 * need.kv.n_kv_heads * need.kv.head_dim * itemsize
+            v_heads, v_dim = need.kv.value_shape
+            total += (need.kv.n_kv_heads * need.kv.head_dim + v_heads * v_dim) * itemsize
     return total
 
 

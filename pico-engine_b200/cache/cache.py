@@ -11,7 +11,10 @@ sequence.
 * A group with a window gives a page back as soon as all its positions lie before every
   window that a later token can have, so in steady state it holds about ``window`` positions
   per sequence.
-* State: ``state [entry with state, slot, elems]`` float32, zeroed when a slot is taken.
+* State: ``state [entry with state, slot, elems]`` (float32 unless the mixer asks otherwise), zeroed when a slot is taken.
+* Values may have another head size and another number of heads than keys (``KVNeed.v_head_dim``, ``v_heads``): the
+  pools are then shaped accordingly (this library's attention kernels take equal shapes; a mixer that asks for
+  others brings the kernel that reads them).
 * Beside what sequences hold there is one *idle* slot with one page in every group (``idle_slot``,
   ``idle_page``: the index after the last real one): a step that is padded to a fixed number of rows
   (a captured decode step of a bucket of rows) lets its idle rows read and write there, so that
@@ -49,7 +52,7 @@ class KVGroup:
     table: Dict[int, List[int]]           # slot -> physical page of each logical page (-1: given back)
 
     def bytes(self) -> int:
-        return 0 if self.k is None else 2 * self.k.numel() * self.k.element_size()      # with the idle page
+        return 0 if self.k is None else (self.k.numel() + self.v.numel()) * self.k.element_size()      # with the idle page
 
 
 class Cache:
@@ -85,11 +88,16 @@ class Cache:
         self.idle_slot, self.idle_page = max_seqs, self.n_pages       # one past the slots and pages that sequences use
         if allocate:
             for g in self.groups:
-                shape = (len(g.entries), self.n_pages + 1, g.need.n_kv_heads, PAGE, g.need.head_dim)
-                g.k = torch.zeros(shape, dtype=dtype, device=self.device)
-                g.v = torch.zeros(shape, dtype=dtype, device=self.device)
+                v_heads, v_dim = g.need.value_shape
+                g.k = torch.zeros((len(g.entries), self.n_pages + 1, g.need.n_kv_heads, PAGE, g.need.head_dim),
+                                  dtype=dtype, device=self.device)
+                g.v = torch.zeros((len(g.entries), self.n_pages + 1, v_heads, PAGE, v_dim), dtype=dtype, device=self.device)
             for e in self.state_entries:
-                self.state[e] = torch.zeros(max_seqs + 1, needs[e].state_elems, dtype=torch.float32, device=self.device)
+                kind = needs[e].state_dtype
+                if kind not in ("float32", "bfloat16", "engine"):
+                    raise ValueError(f"schedule entry {e}: state_dtype must be float32, bfloat16 or engine, not {kind!r}")
+                sd = dtype if kind == "engine" else getattr(torch, kind)
+                self.state[e] = torch.zeros(max_seqs + 1, needs[e].state_elems, dtype=sd, device=self.device)
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -179,7 +187,7 @@ class Cache:
         return self.state.get(entry)
 
     def bytes(self) -> int:
-        return sum(g.bytes() for g in self.groups) + sum(t.numel() * 4 for t in self.state.values())
+        return sum(g.bytes() for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values())
 
     def check(self) -> None:
         """Invariants of the bookkeeping: nothing lost, nothing held twice."""

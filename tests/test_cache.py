@@ -143,3 +143,21 @@ def test_random_traffic_keeps_the_books():
         c.close(s)
     c.check()
     assert c.slots.free_count == 6 and all(g.pages.free_count == g.pages.n for g in c.groups)
+
+
+def test_values_and_state_may_be_shaped_otherwise():
+    """Keys and values need not have the same heads and head size (a cache of one compressed row per position keeps
+    no values at all), and a mixer may ask for its state in another dtype."""
+    needs_ = [CacheNeeds(kv=KVNeed(2, 16, None, v_head_dim=24)), CacheNeeds(kv=KVNeed(1, 40, None, v_heads=0)),
+              CacheNeeds(kv=KVNeed(2, 16, None, v_head_dim=24), state_elems=6, state_dtype="bfloat16"),
+              CacheNeeds(state_elems=3, state_dtype="engine")]
+    c = Cache(needs_, max_tokens=128, max_seqs=2, dtype=torch.float32, device="cpu")
+    assert len(c.groups) == 2 and c.groups[0].entries == [0, 2]
+    k, v = c.pools(2)
+    assert k.shape == (3, 2, PAGE, 16) and v.shape == (3, 2, PAGE, 24)
+    k, v = c.pools(1)
+    assert k.shape == (3, 1, PAGE, 40) and v.numel() == 0
+    assert c.state_of(2).dtype == torch.bfloat16 and c.state_of(3).dtype == torch.float32 and c.state_of(3).shape == (3, 3)
+    assert c.bytes() == 4 * (2 * 3 * PAGE * (2 * 16 + 2 * 24) + 3 * PAGE * 40) + 3 * 6 * 2 + 3 * 3 * 4
+    with pytest.raises(ValueError, match="state_dtype"):
+        Cache([CacheNeeds(state_elems=2, state_dtype="int8")], 64, 1, torch.float32, "cpu")
