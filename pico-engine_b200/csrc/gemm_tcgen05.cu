@@ -31,7 +31,7 @@
 // pico-engine leaves these products to cuBLAS under fp16 autocast and runs bias, rotation, cache write,
 // residual and activation as separate launches (src/pico_engine/model.py:177-235, kernels.py:37-87).
 #include "common.cuh"
-#include <cuda.h>
+#include "tensor_map.cuh"
 
 #define GT_BK 64
 #define GT_EPI_WARPS 16
@@ -668,33 +668,8 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_pair_kernel(const __g
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*gt_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static gt_encode_fn gt_encoder() {
-    static gt_encode_fn fn = nullptr;
-    if (!fn) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (gt_encode_fn)sym;
-    }
-    return fn;
-}
-
-// a [rows, cols] row-major matrix, loaded (or reduced into) in boxes of box_cols x box_rows with 128-byte swizzle
 static int gt_make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows, int box_cols, bool f32) {
-    gt_encode_fn enc = gt_encoder();
-    if (!enc) return PE_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * (f32 ? 4 : 2)};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
-                           dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
+    return pe_tensor_map_2d(map, base, rows, cols, box_rows, box_cols, f32);
 }
 
 static int gt_sm_count() {

@@ -451,19 +451,44 @@ def check_status(device) -> None:
 FUSED_MAX_WEIGHT_BYTES = int(os.environ.get("PICO_ENGINE_FUSED_MAX_MB", "100")) << 20
 
 
-def fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor) -> bool:
+def fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor, max_rows: int = FUSED_MAX_ROWS) -> bool:
     """Whether the fused decode kernels take a product with ``rows`` rows and weight ``w``."""
-    return (rows <= FUSED_MAX_ROWS and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.is_contiguous()
+    return (rows <= max_rows and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.is_contiguous()
             and w.data_ptr() % 16 == 0 and all(t.is_contiguous() and t.data_ptr() % 16 == 0 for t in others)
             and w.numel() * 2 <= FUSED_MAX_WEIGHT_BYTES)
+
+
+# The same fused products for 17 to 64 rows are another kernel (csrc/linear_batch.cu: 64 rows of the weight a CTA
+# instead of 16, operands through shared memory by TMA); the three functions below take either number of rows.
+# It is not what a decode step of that many rows runs unless PICO_ENGINE_BATCH_FUSED=1: measured on a B200 at the
+# Qwen2.5-0.5B widths and 64 rows, in captured graphs, norm + q/k/v + rotation take 10.9 us in it against 7.5 us as
+# three kernels around the library's product, the output projection 6.5 against 5.3, norm + gate/up + SwiGLU 25.6
+# against 9.1, the down projection 9.7 against 10.1; at the 7B widths it streams weights at 1.2 to 2.1 TB/s where
+# the library reaches 4 to 5.  Two things bound it: mma.sync runs at about a quarter of the tcgen05 rate (1,000
+# cycles for a chunk of 128 columns), and every CTA converts the float32 rows of the residual stream itself, which
+# for gate/up (152 CTAs x 229 KB) is all the L2 delivers.
+BATCH_MAX_ROWS = 64
+BATCH_ENABLED = os.environ.get("PICO_ENGINE_BATCH_FUSED", "0") == "1"
+
+
+def decode_fused_takes(rows: int, w: torch.Tensor, *others: torch.Tensor) -> bool:
+    """Whether a decode step of ``rows`` sequences can run this product fused with its neighbours."""
+    return fused_takes(rows, w, *others, max_rows=BATCH_MAX_ROWS if BATCH_ENABLED else FUSED_MAX_ROWS)
+
+
+def set_batch_fused(on: bool) -> bool:
+    """Let decode steps of 17 to 64 rows run the fused products of csrc/linear_batch.cu (or not); returns what was set."""
+    global BATCH_ENABLED
+    was, BATCH_ENABLED = BATCH_ENABLED, bool(on)
+    return was
 
 
 def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
                  norm_of: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
                  eps: float = 0.0) -> torch.Tensor:
-    """a [M <= 16, K] . w [N, K]^T (+ bias); with ``norm_of`` (float32 [M, K]) the operand is
-    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``."""
+    """a [M <= 64, K] . w [N, K]^T (+ bias); with ``norm_of`` (float32 [M, K]) the operand is
+    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``.  (More than 16 rows: bfloat16 or accumulated results.)"""
     src = norm_of if norm_of is not None else a
     M, K = src.shape
     N = w.shape[0]
@@ -480,22 +505,22 @@ def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torc
     else:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=w.device)
         epilogue = _EPILOGUE_STORE[out.dtype]
-    check(core().pe_linear_fused(_ptr(a), _ptr(norm_of), _ptr(norm_weight),
-                                 0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
-                                 w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
-                                 epilogue, M, N, K, status_ptr(w.device), stream_ptr()), "linear_fused")
+    fn, name = (core().pe_linear_fused, "linear_fused") if M <= FUSED_MAX_ROWS else (core().pe_linear_batch, "linear_batch")
+    check(fn(_ptr(a), _ptr(norm_of), _ptr(norm_weight), 0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
+             w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
+             epilogue, M, N, K, status_ptr(w.device), stream_ptr()), name)
     return out
 
 
 def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(h Wg^T) * (h Wu^T) with h = RMSNorm(x); x float32 [M <= 16, K], w_gate_up [2I, K] (gate rows first)."""
+    """silu(h Wg^T) * (h Wu^T) with h = RMSNorm(x); x float32 [M <= 64, K], w_gate_up [2I, K] (gate rows first)."""
     M, K = x.shape
     I = w_gate_up.shape[0] // 2
     _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
     act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
-    check(core().pe_norm_gate_up_swiglu(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
-                                        w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_ptr(x.device),
-                                        stream_ptr()), "norm_gate_up_swiglu")
+    fn = core().pe_norm_gate_up_swiglu if M <= FUSED_MAX_ROWS else core().pe_batch_norm_gate_up_swiglu
+    check(fn(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
+             w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_ptr(x.device), stream_ptr()), "norm_gate_up_swiglu")
     return act
 
 
@@ -521,11 +546,14 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
         if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim):
             raise KernelError(f"cache pool must be [pages, {n_kv}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
     q = torch.empty(M, n_q * head_dim, dtype=torch.bfloat16, device=x.device)
-    check(core().pe_norm_qkv_rope_store(None, x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"),
-                                        float(eps), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
-                                        q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
-                                        tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
-                                        1 if store else 0, status_ptr(x.device), stream_ptr()), "norm_qkv_rope_store")
+    tail = (q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(k_pool),
+            _ptr(v_pool), _ptr(block_table), table_stride, 1 if store else 0, status_ptr(x.device), stream_ptr())
+    head = (x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps), w_qkv.data_ptr(), _ptr(b_qkv),
+            0 if b_qkv is None else _code(b_qkv, "b_qkv"))
+    if M <= FUSED_MAX_ROWS:
+        check(core().pe_norm_qkv_rope_store(None, *head, *tail), "norm_qkv_rope_store")
+    else:
+        check(core().pe_batch_norm_qkv_rope_store(*head, *tail), "batch_norm_qkv_rope_store")
     return q
 
 

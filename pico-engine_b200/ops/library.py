@@ -12,7 +12,7 @@ from ..csrc import build
 P, I, F, LL, ULL = c_void_p, c_int, c_float, c_longlong, c_ulonglong
 
 CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_mma.cu",
-                "linear_fused.cu", "gemm_tcgen05.cu")
+                "linear_fused.cu", "linear_batch.cu", "gemm_tcgen05.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -34,6 +34,9 @@ _SIGNATURES = {
     "pe_gemm_tcgen05_rope": [P, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P, P],
     "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
     "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
+    "pe_linear_batch": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
+    "pe_batch_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
+    "pe_batch_norm_qkv_rope_store": [P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
     "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
 }
 

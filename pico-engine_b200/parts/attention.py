@@ -104,7 +104,7 @@ class GQAAttention(Mixer):
         from .position import NoPosition, RotaryHalf
         return (ctx.dtype == torch.bfloat16 and type(norm) is RMSNorm and type(self.position) in (RotaryHalf, NoPosition)
                 and (self.b_qkv is None or self.b_qkv.dtype in (torch.bfloat16, torch.float32))
-                and kernels.fused_takes(x.shape[0], self.w_qkv, x) and kernels.fused_takes(x.shape[0], self.w_o))
+                and kernels.decode_fused_takes(x.shape[0], self.w_qkv, x) and kernels.decode_fused_takes(x.shape[0], self.w_o))
 
     takes_pending = True
 

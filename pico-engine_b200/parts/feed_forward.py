@@ -42,7 +42,7 @@ class SwiGLU(FeedForward):
     def add_to(self, x, norm, ctx):
         from .norm import RMSNorm
         if (ctx.dtype == torch.bfloat16 and type(norm) is RMSNorm and self.spec.intermediate % 8 == 0
-                and kernels.fused_takes(x.shape[0], self.w_gate_up, x) and kernels.fused_takes(x.shape[0], self.w_down)):
+                and kernels.decode_fused_takes(x.shape[0], self.w_gate_up, x) and kernels.decode_fused_takes(x.shape[0], self.w_down)):
             # decoding a few sequences: norm, gate and up products and the activation are one kernel
             ctx.settle(x)
             act = kernels.norm_gate_up_swiglu(x, norm.weight, norm.eps, self.w_gate_up)

@@ -86,6 +86,24 @@ def test_one_token_steps_of_many_rows(models, name, dtype, batch_size):
     replay.compare(replay.run_in_process(eng, steps), replay.plain_logits(cfg, w, reqs), dtype, f"batched by {batch_size}")
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("batch_size", [24, 64])
+def test_one_token_steps_of_many_rows_with_their_fused_products(models, name, batch_size):
+    """The same with the fused products for 17 to 64 rows switched on (csrc/linear_batch.cu, off unless asked for):
+    prompt steps of up to 64 tokens take them too."""
+    from pico_engine.ops import kernels
+    eng, cfg, w = models[(name, "bfloat16")]
+    reqs = many_short_requests(cfg, name, batch_size + 9, 30 + batch_size)
+    steps = replay.batched(reqs, batch_size, 0.5)
+    was = kernels.set_batch_fused(True)
+    try:
+        got = replay.run_in_process(eng, steps)
+        kernels.check_status("cuda")
+    finally:
+        kernels.set_batch_fused(was)
+    replay.compare(got, replay.plain_logits(cfg, w, reqs), "bfloat16", f"batched by {batch_size}, fused")
+
+
 PIECE_LENGTHS = {"A": [100, 7, 64, 33, 128], "B": [200, 9, 130, 64, 256], "C": [300, 20, 150, 257, 129]}
 
 

@@ -663,6 +663,99 @@ def test_norm_qkv_rope_store(K, nq, nkv, hd, H, theta, rotate):
     assert float(kp.abs().sum()) == 0.0
 
 
+# ---------------------------------------------------------------------------- the same for 17 to 64 rows (csrc/linear_batch.cu)
+
+@pytest.mark.parametrize("M", [17, 32, 33, 47, 64])
+@pytest.mark.parametrize("N,K_", [(100, 96), (896, 896), (896, 4864), (9728, 896), (70, 168), (1000, 3584),
+                                  (40, 9000), (136, 72), (264, 200),      # K ends in the middle of a 16-column step
+                                  (4744, 512)])
+def test_linear_batch(K, M, N, K_):
+    a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
+    want = a.double() @ w.double().T
+    A, W = dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16))
+    assert K.fused_takes(M, W, A, max_rows=K.BATCH_MAX_ROWS) and not K.fused_takes(M, W, A)
+    x = rnd(M, N, seed=4)
+    got = K.linear_fused(A, W, accumulate_into=dev(x.clone()))
+    K.check_status("cuda")
+    err, at = rel_err(got, x.double() + want)
+    assert err < 2e-5, (err, at)
+    got = K.linear_fused(A, W, dev(b.to(torch.float32)), accumulate_into=dev(x.clone()))
+    err, at = rel_err(got, x.double() + want + b.double())
+    assert err < 2e-5, (err, at)
+    got = K.linear_fused(A, W, dev(b.to(torch.bfloat16)), out_dtype=torch.bfloat16)
+    err, at = rel_err(got.float(), want + b.double())
+    assert got.shape == (M, N) and err < 5e-3, (err, at)
+    # the operand as the RMSNorm of float32 rows
+    xs, nw = rnd(M, K_, seed=5, scale=2.0), bf(1 + rnd(K_, seed=6) * 0.1)
+    h = plain.rms_norm(xs, nw, 1e-5).to(torch.bfloat16).double()
+    for nw_dtype in (torch.bfloat16, torch.float32):
+        got = K.linear_fused(None, W, accumulate_into=dev(x.clone()), norm_of=dev(xs), norm_weight=dev(nw.to(nw_dtype)), eps=1e-5)
+        K.check_status("cuda")
+        assert torch.allclose(got.cpu().double(), x.double() + h @ w.double().T, atol=3e-2, rtol=1e-2)   # a bfloat16 rounding of h may flip
+
+
+def test_linear_batch_rows_do_not_depend_on_their_neighbours(K):
+    a, w = bf(rnd(64, 4864, seed=1)), bf(rnd(896, 4864, seed=2, scale=0.02))
+    W = dev(w.to(torch.bfloat16))
+    zero = lambda n: torch.zeros(n, 896, dtype=torch.float32, device="cuda")
+    whole = K.linear_fused(dev(a.to(torch.bfloat16)), W, accumulate_into=zero(64))
+    for rows in (list(range(20)), list(range(3, 64, 2)), list(range(40, 64)) + list(range(10))):
+        assert torch.equal(K.linear_fused(dev(a[rows].to(torch.bfloat16)), W, accumulate_into=zero(len(rows))), whole[rows])
+
+
+@pytest.mark.parametrize("M,H,I", [(17, 64, 160), (64, 896, 4864), (40, 96, 352), (33, 3584, 1000), (24, 512, 2504), (32, 200, 72)])
+def test_batch_norm_gate_up_swiglu(K, M, H, I):
+    x, nw = rnd(M, H, seed=1, scale=2.0), bf(1 + rnd(H, seed=2) * 0.1)
+    w = bf(rnd(2 * I, H, seed=3, scale=H ** -0.5))
+    h = plain.rms_norm(x, nw, 1e-6).to(torch.bfloat16).float()
+    gu = (h @ w.T).to(torch.bfloat16).float()
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    got = K.norm_gate_up_swiglu(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)))
+    K.check_status("cuda")
+    assert got.shape == (M, I) and torch.allclose(got.float().cpu(), want, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("nq,nkv,hd,H,theta,rotate", [(4, 2, 16, 64, 1e4, True), (3, 1, 32, 96, 1e6, True), (14, 2, 64, 896, 1e6, True),
+                                                       (5, 5, 48, 240, 1e4, False), (7, 1, 128, 200, 1e6, True), (28, 4, 128, 3584, 1e6, True)])
+def test_batch_norm_qkv_rope_store(K, M, nq, nkv, hd, H, theta, rotate):
+    """Tokens of several sequences in one step, some sequences with several tokens (a short prompt step)."""
+    g = torch.Generator().manual_seed(M)
+    row = torch.sort(torch.randint(0, 9, (M,), generator=g)).values.to(torch.int32)
+    first = torch.tensor([62, 5, 63, 64, 0, 100, 17, 30, 1], dtype=torch.int32)
+    pos = torch.zeros(M, dtype=torch.int32)
+    for m in range(M):                                            # consecutive positions within a sequence
+        pos[m] = first[row[m]] + int((row[:m] == row[m]).sum())
+    x, nw = rnd(M, H, seed=1, scale=2.0), bf(1 + rnd(H, seed=2) * 0.1)
+    w, b = bf(rnd((nq + 2 * nkv) * hd, H, seed=3, scale=H ** -0.5)), bf(rnd((nq + 2 * nkv) * hd, seed=4, scale=0.3))
+    cos, sin = plain.rope_angles(torch.arange(200), hd, theta)
+    table = torch.arange(9 * 3, dtype=torch.int32).flip(0).view(9, 3).contiguous()
+    kp = torch.zeros(9 * 3, nkv, PAGE, hd, dtype=torch.bfloat16, device="cuda")
+    vp = torch.zeros_like(kp)
+    q = K.norm_qkv_rope_store(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)), dev(b.to(torch.float32)),
+                              nq, nkv, hd, dev(cos) if rotate else None, dev(sin) if rotate else None, dev(pos), dev(row),
+                              kp, vp, dev(table), 3)
+    K.check_status("cuda")
+    h = plain.rms_norm(x, nw, 1e-6).to(torch.bfloat16).float()
+    qkv = (h @ w.T + b).to(torch.bfloat16).float()
+    qk = qkv[:, :(nq + nkv) * hd].view(M, nq + nkv, hd)
+    if rotate:
+        qk = plain.apply_rope(qk, cos[pos.long()], sin[pos.long()])
+    v = qkv[:, (nq + nkv) * hd:].view(M, nkv, hd)
+    assert torch.allclose(q.float().cpu().view(M, nq, hd), qk[:, :nq], atol=4e-2, rtol=2e-2)
+    kc, vc = kp.float().cpu(), vp.float().cpu()
+    for m in range(M):
+        p_ = int(pos[m])
+        pg = int(table[int(row[m]), p_ // PAGE])
+        assert torch.allclose(kc[pg, :, p_ % PAGE], qk[m, nq:], atol=4e-2, rtol=2e-2), m
+        assert torch.allclose(vc[pg, :, p_ % PAGE], v[m], atol=4e-2, rtol=2e-2), m
+    assert int((kc != 0).any(dim=-1).sum()) == M * nkv and int((vc != 0).any(dim=-1).sum()) == M * nkv
+    kp.zero_()
+    K.norm_qkv_rope_store(dev(x), dev(nw.to(torch.bfloat16)), 1e-6, dev(w.to(torch.bfloat16)), None, nq, nkv, hd,
+                          None, None, dev(pos), dev(row), None, None, dev(table), 3)
+    assert float(kp.abs().sum()) == 0.0
+
+
 # ---------------------------------------------------------------------------- tcgen05 products for more than 16 rows
 
 ORIENTATIONS = ["rows", "pairs", "swapped"]       # 128 rows of a CTA / 256 rows of a CTA pair / rows of the weight on the lanes
