@@ -20,7 +20,8 @@
 // rows are brought into shared memory by bulk asynchronous copies (cp.async.bulk, the 1-D TMA
 // path, completing on an mbarrier), one copy per row and chunk of up to 1024 columns, up to
 // four chunks in flight; registers hold none of it, so many CTAs are resident and the whole
-// matrix can be under way at once.  The copies are issued before the kernel waits for its
+// matrix can be under way at once.  The rows are dealt out to all eight warps, four to each: a warp issues
+// its copies one after the other, at about 65 cycles a copy.  The copies are issued before the kernel waits for its
 // predecessor (griddepcontrol.wait): no kernel writes weights.  The roles of the MMA operands
 // are swapped as in linear_mma.cu: rows of W are the M side of mma.sync m16n8k16, sequences
 // the N side; the warps take the 32-wide k steps of a chunk in turn and add their partial sums
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
             for (unsigned o = 0; o < row_bytes; o += 16)
                 *reinterpret_cast<uint4*>(lf_smem + s * stage_bytes + lane * row_bytes + o) = make_uint4(0u, 0u, 0u, 0u);
     }
-    const bool my_a_ok = lane < a_rows && lane < M;          // warp 1: lane m copies row m of A
+    const bool my_a_ok = lane < a_rows && lane < M;          // row m of A is copied (else it reads as zeros)
     if (warp == 2 && lane < a_rows && !my_a_ok) {
         for (int s = 0; s < stages; ++s)
             for (unsigned o = 0; o < row_bytes; o += 16)
@@ -188,35 +189,42 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
     __syncthreads();
     if (ksplit > 1) lf_cluster_arrive();                     // waited for before the first write to another CTA
 
-    // chunk c of every valid row into stage c % stages; called by all of warp 0
+    // Chunk c of every valid row into stage c % stages; called by all threads.  A thread's bulk copies are issued one
+    // after the other at about 65 cycles each (measured), the lanes of a warp instruction too, so the rows are dealt out
+    // to the warps: lanes 0-3 of warp w copy rows 4 w .. 4 w + 3 of W, lanes 4-5 rows 2 w, 2 w + 1 of the activations.
+    const int cp_r = lane < 4 ? warp * 4 + lane : -1;
+    const int cp_rt = cp_r >> 4, cp_l = cp_r & 15;
+    const int cp_row = cp_r < 0 ? -1 : cp_l < 8 ? lo_base + cp_rt * rt_step + cp_l : (hi_base < 0 ? -1 : hi_base + cp_rt * rt_step + cp_l - 8);
+    const bool cp_ok = cp_r >= 0 && cp_r < tile_rows && cp_row >= 0 && cp_row < p.N && (EPI != LF_SWIGLU || cp_l >= 8 || cp_row < p.I);
+    const unsigned n_ok = __popc(__ballot_sync(0xffffffffu, my_row_ok));
     auto issue = [&](int c) {
         const int k0 = c * chunk, cols = min(chunk, K - k0);
         const unsigned bar = bar0 + 8u * (c % stages);
-        const unsigned n_ok = __popc(__ballot_sync(0xffffffffu, my_row_ok));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of the stage precede its refill
-        if (lane == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
-        __syncwarp();
-        if (my_row_ok)
-            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + lane * row_bytes, p.W + (size_t)my_row * p.K + k_begin + k0,
+        if (threadIdx.x == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
+        if (cp_ok) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of the stage precede its refill
+            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + cp_r * row_bytes, p.W + (size_t)cp_row * p.K + k_begin + k0,
                          (unsigned)cols * 2u, bar);
+        }
     };
 
-    // the same for the activations (PLAIN only); called by all of warp 1, after the wait for the predecessor
+    // the same for the activations (PLAIN only), after the wait for the predecessor
+    const int cp_a = (lane == 4 || lane == 5) ? warp * 2 + lane - 4 : -1;
+    const bool cp_a_ok = cp_a >= 0 && cp_a < a_rows && cp_a < M;
+    const unsigned n_a_ok = __popc(__ballot_sync(0xffffffffu, my_a_ok));
     auto issue_a = [&](int c) {
         const int k0 = c * chunk, cols = min(chunk, K - k0);
         const unsigned bar = bar_a0 + 8u * (c % stages);
-        const unsigned n_ok = __popc(__ballot_sync(0xffffffffu, my_a_ok));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (lane == 0) lf_bar_expect(bar, n_ok * (unsigned)cols * 2u);
-        __syncwarp();
-        if (my_a_ok)
-            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + (tile_rows + lane) * row_bytes, p.A + (size_t)lane * p.K + k_begin + k0,
+        if (threadIdx.x == 0) lf_bar_expect(bar, n_a_ok * (unsigned)cols * 2u);
+        if (cp_a_ok) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            lf_bulk_copy(smem0 + (c % stages) * stage_bytes + (tile_rows + cp_a) * row_bytes, p.A + (size_t)cp_a * p.K + k_begin + k0,
                          (unsigned)cols * 2u, bar);
+        }
     };
 
     pdl_launch_dependents();
-    if (warp == 0)                                           // W first: no kernel writes it, so it need not wait
-        for (int c = 0; c < n_chunks && c < stages; ++c) issue(c);
+    for (int c = 0; c < n_chunks && c < stages; ++c) issue(c);      // W first: no kernel writes it, so it need not wait
     // ROPE: what the epilogue needs of the step's description (positions, pages) and of the rotation tables is
     // asked for now: none of it is written by a kernel of the step, and the epilogue then waits for no load.
     int ep_pos = 0, ep_page = -1;
@@ -233,7 +241,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
         }
     }
     pdl_wait();                                              // from here on the preceding kernel's results may be read
-    if (PRO == LF_PLAIN && warp == 1)
+    if (PRO == LF_PLAIN)
         for (int c = 0; c < n_chunks && c < stages; ++c) issue_a(c);
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
@@ -331,8 +339,8 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
         }
         if (c + stages < n_chunks) {                         // the stage is free again: refill it
             __syncthreads();
-            if (warp == 0) issue(c + stages);
-            if (PRO == LF_PLAIN && warp == 1) issue_a(c + stages);
+            issue(c + stages);
+            if (PRO == LF_PLAIN) issue_a(c + stages);
         }
     }
 
