@@ -37,8 +37,8 @@
 #include "common.cuh"
 
 #define LF_WARPS 8
-#define LF_UNROLL 4
-#define LF_MAX_CHUNK 1024            // columns of W per bulk copy
+#define LF_UNROLL(NT) ((NT) == 1 ? 4 : 2)   // k steps of a chunk a warp takes: what its registers hold of the activations
+#define LF_MAX_CHUNK 1024            // columns of W per bulk copy (LF_WARPS * LF_UNROLL * 32 at most)
 #define LF_MAX_STAGES 4              // chunks in flight: as many as fit in 160 KB of shared memory, at most twice this
 #define LF_ROW_PAD 8                 // bfloat16 of padding per row in shared memory: skews the banks
 #define LF_WAIT_CYCLES 2000000000ll    // about a second of SM clock: the longest a CTA waits for its own copies
@@ -124,7 +124,7 @@ __device__ __forceinline__ unsigned lf_pack(float lo, float hi) {
 // CTAs resident per SM that the register budget is set for: the products with many tiles (gate and up,
 // the vocabulary) want as many as their shared memory allows; q/k/v has fewer tiles than the GPU has SMs
 // and takes the registers instead.
-#define LF_MIN_CTAS(NT, RT, EPI) (((EPI) == LF_ROPE || (RT) == 2) ? ((NT) == 1 ? 3 : 2) : ((NT) == 1 ? 5 : 3))
+#define LF_MIN_CTAS(NT, RT, EPI) ((RT) == 2 ? 3 : (EPI) == LF_ROPE ? ((NT) == 1 ? 3 : 2) : ((NT) == 1 ? 5 : 3))
 
 // NT: 8-row tiles of sequences (M <= 8 * NT); RT: 16-row tiles of W a CTA takes (2 where a product has
 // so many tiles that the activations, which every CTA reads, would cost as much as the weights);
@@ -133,7 +133,6 @@ template <int NT, int RT, int PRO, int EPI, bool SPLIT>
 __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linear_fused_kernel(const LfArgs p, int* status) {
     extern __shared__ __align__(128) unsigned char lf_smem[];   // [stage][16 * RT rows][chunk + pad] bfloat16
     __shared__ __align__(8) unsigned long long bars[2 * LF_MAX_STAGES], bars_a[2 * LF_MAX_STAGES], bar_x;
-    __shared__ float red[LF_WARPS][RT * NT * 4][32];
     __shared__ float ssq[LF_WARPS][NT * 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int M = p.M;
@@ -161,7 +160,13 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
     const unsigned smem0 = lf_smem_addr(lf_smem), bar0 = lf_smem_addr(bars), bar_a0 = lf_smem_addr(bars_a);
     const unsigned bar_x0 = lf_smem_addr(&bar_x);
     // what the other ranges send: [range - 1][item][low sum, high sum, sum of squares], behind the stages
-    float* gather = reinterpret_cast<float*>(lf_smem + (size_t)stages * stage_bytes);
+    // The warps' partial sums.  For 9 to 16 rows (16 KB with two row tiles) they take the place of the stages once every
+    // warp is done with them, so that three CTAs fit an SM; for up to 8 rows they have their own array and no warp waits.
+    constexpr bool RED_IN_RING = NT > 1;
+    __shared__ float red_own[RED_IN_RING ? 1 : LF_WARPS][RT * NT * 4][32];
+    float (*red)[RT * NT * 4][32] = RED_IN_RING ? reinterpret_cast<float (*)[RT * NT * 4][32]>(lf_smem) : red_own;
+    constexpr unsigned RED_BYTES = RED_IN_RING ? LF_WARPS * RT * NT * 4 * 32 * 4 : 0;
+    float* gather = reinterpret_cast<float*>(lf_smem + max((unsigned)stages * stage_bytes, RED_BYTES));
 
     // row rr of the tile in shared memory (16 a tile: 8 of group lo, 8 of group hi) holds this row of W, or zeros
     const int my_rt = lane >> 4, my_l = lane & 15;
@@ -257,12 +262,12 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[rt][j][0] = acc[rt][j][1] = acc[rt][j][2] = acc[rt][j][3] = 0.f;
 
-    // the activations of this warp's steps of chunk c (a chunk has at most LF_WARPS * LF_UNROLL steps)
-    auto load_a = [&](int c, uint4 (&a)[LF_UNROLL][NT]) {
+    // the activations of this warp's steps of chunk c (a chunk has at most LF_WARPS * LF_UNROLL(NT) steps)
+    auto load_a = [&](int c, uint4 (&a)[LF_UNROLL(NT)][NT]) {
         const int k0 = c * chunk, cols = min(chunk, K - k0);
 #pragma unroll
-        for (int u = 0; u < LF_UNROLL; ++u) {
-            const int col = (warp + u * LF_WARPS) * 32 + t * 8, k = k_begin + k0 + col;
+        for (int u = 0; u < LF_UNROLL(NT); ++u) {
+            const int col = (((warp - k0 / 32) & (LF_WARPS - 1)) + u * LF_WARPS) * 32 + t * 8, k = k_begin + k0 + col;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int m = j * 8 + g;
@@ -296,21 +301,22 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
         }
     };
 
-    uint4 a_cur[LF_UNROLL][NT], a_next[LF_UNROLL][NT];
+    uint4 a_cur[LF_UNROLL(NT)][NT], a_next[LF_UNROLL(NT)][NT];
     if (PRO == LF_RMSNORM) load_a(0, a_cur);
     for (int c = 0; c < n_chunks; ++c) {
         const int k0 = c * chunk, cols = min(chunk, K - k0), steps = (cols + 31) / 32;
         const unsigned stage = smem0 + (c % stages) * stage_bytes;
         if (PRO == LF_RMSNORM) load_a(c + 1, a_next);        // in flight while this chunk's W is awaited and used
         const unsigned parity = (unsigned)(c / stages) & 1u;
-        if (warp < steps && !(lf_bar_wait(bar0 + 8u * (c % stages), parity) &&
+        const int first = (warp - k0 / 32) & (LF_WARPS - 1);     // this warp's k steps: those of the range that are = warp mod 8,
+        if (first < steps && !(lf_bar_wait(bar0 + 8u * (c % stages), parity) &&
                               (PRO != LF_PLAIN || lf_bar_wait(bar_a0 + 8u * (c % stages), parity)))) {
             atomicExch(status, 1);                           // the copies did not arrive: give up, loudly
             return;
         }
 #pragma unroll
-        for (int u = 0; u < LF_UNROLL; ++u) {
-            const int step = warp + u * LF_WARPS, col = step * 32 + t * 8;
+        for (int u = 0; u < LF_UNROLL(NT); ++u) {
+            const int step = first + u * LF_WARPS, col = step * 32 + t * 8;   // however the range is cut into chunks (the sums do not depend on the cut)
             if (step < steps) {                              // the same for all lanes of the warp: the MMA needs them all
                 const bool in = col < cols;                  // a last step may be narrower than 32 columns
                 uint4 wa[RT], wb[RT];
@@ -333,7 +339,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
         }
         if (PRO == LF_RMSNORM) {
 #pragma unroll
-            for (int u = 0; u < LF_UNROLL; ++u)
+            for (int u = 0; u < LF_UNROLL(NT); ++u)
 #pragma unroll
                 for (int j = 0; j < NT; ++j) a_cur[u][j] = a_next[u][j];
         }
@@ -345,6 +351,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
     }
 
     // acc[rt][j][e] of lane (g, t): MMA row g (+8 if e & 2) of tile rt, sequence j*8 + 2t + (e & 1)
+    if (RED_IN_RING) __syncthreads();                        // every warp has read what it needs of the stages
 #pragma unroll
     for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
@@ -497,22 +504,43 @@ static int lf_launch(LfArgs& a, int tiles, int* status, cudaStream_t s) {
     // Chunks of equal length (a short last chunk costs a whole turn of the pipeline).  A range of K that fits
     // one chunk is one chunk.  A longer one is cut so that a stage is about lf_stage_kb() and a CTA holds about
     // lf_budget_kb(): several CTAs then share an SM and stream while another starts up or runs its epilogue.
-    int cap = LF_MAX_CHUNK;
+    const int max_chunk = LF_WARPS * LF_UNROLL(nt) * 32;
+    int cap = max_chunk;
     size_t budget = 160u << 10;
     if (a.kc > LF_MAX_CHUNK && lf_stage_kb() > 0) {
         cap = ((lf_stage_kb() << 10) / (rows_total * 2) - LF_ROW_PAD) / 32 * 32;
         if (cap < 128) cap = 128;
-        if (cap > LF_MAX_CHUNK) cap = LF_MAX_CHUNK;
+        if (cap > max_chunk) cap = max_chunk;
         budget = (size_t)lf_budget_kb() << 10;
     }
-    const int n_chunks = (a.kc + cap - 1) / cap;
-    a.chunk = ((a.kc + n_chunks - 1) / n_chunks + 31) / 32 * 32;
-    const size_t stage = (size_t)rows_total * (a.chunk + LF_ROW_PAD) * 2;
-    int max_stages = (int)(budget / stage);                  // chunks in flight: what fits the budget, at most 8
-    if (max_stages > 2 * LF_MAX_STAGES) max_stages = 2 * LF_MAX_STAGES;
-    if (max_stages < 1) max_stages = 1;
-    a.stages = n_chunks < max_stages ? n_chunks : max_stages;
-    const size_t smem = (size_t)a.stages * stage + (size_t)(a.ksplit - 1) * nt * 64 * 3 * 4;
+    const size_t gather_bytes = (size_t)(a.ksplit - 1) * nt * 64 * 3 * 4;
+    const size_t red_all = (size_t)LF_WARPS * (two ? 2 : 1) * nt * 4 * 32 * 4;                   // the warps' partial sums:
+    const size_t red_bytes = nt > 1 ? red_all : 0, red_static = nt > 1 ? 0 : red_all;            // in the stages' place, or an array of their own
+    auto shape = [&](int cap_, size_t budget_, size_t* ring) {
+        const int n_chunks = (a.kc + cap_ - 1) / cap_;
+        a.chunk = ((a.kc + n_chunks - 1) / n_chunks + 31) / 32 * 32;
+        const size_t stage = (size_t)rows_total * (a.chunk + LF_ROW_PAD) * 2;
+        int max_stages = (int)(budget_ / stage);             // chunks in flight: what fits the budget, at most 8
+        if (max_stages > 2 * LF_MAX_STAGES) max_stages = 2 * LF_MAX_STAGES;
+        if (max_stages < 1) max_stages = 1;
+        a.stages = n_chunks < max_stages ? n_chunks : max_stages;
+        *ring = (size_t)a.stages * stage > red_bytes ? (size_t)a.stages * stage : red_bytes;
+    };
+    size_t ring = 0;
+    shape(cap, budget, &ring);
+    // A grid of two to four CTAs an SM runs as one wave only if that many CTAs fit an SM's 228 KB of shared memory (a
+    // CTA's own, 1 KB that the system keeps for it, 1.5 KB of barriers and sums): measured at 9 to 16 rows, where the
+    // stages are larger, the down projection's 336 CTAs at two an SM took 14.5 us against 9.6.  Where the shape above
+    // does not fit, the stages share what does (two of them at least where K has several chunks).
+    const int grid = (two ? (tiles + 1) / 2 : tiles) * a.ksplit, at_once = (grid + 147) / 148;
+    if (at_once >= 2 && at_once <= 4) {
+        const size_t fits = (size_t)228 * 1024 / at_once - 2560 - gather_bytes - red_static;
+        if (ring > fits) {
+            const int two_fit = (int)(fits / 2 / (rows_total * 2) - LF_ROW_PAD) / 32 * 32;
+            if (two_fit >= 128) shape(two_fit < cap ? two_fit : cap, fits, &ring);
+        }
+    }
+    const size_t smem = ring + gather_bytes;
     constexpr bool can_split = EPI != LF_SWIGLU && EPI != LF_ROPE;
     if (can_split && a.ksplit > 1) {
         if (nt == 1) return lf_launch_nt<1, 1, PRO, EPI, can_split>(a, tiles, smem, status, s);
