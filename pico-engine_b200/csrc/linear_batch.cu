@@ -424,6 +424,8 @@ __global__ void __launch_bounds__(LB_THREADS, 1) linear_batch_kernel(const __gri
 }
 
 // ---------------------------------------------------------------- host side
+extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }     // (this library's own copy of the switch)
+
 static int lb_sm_count() {
     static int n = 0;
     if (!n) {

@@ -9,7 +9,7 @@ from typing import Optional
 
 import torch
 
-from .library import DTYPE_CODE, KernelError, check, core, stream_ptr
+from .library import DTYPE_CODE, KernelError, check, core, extras, stream_ptr
 
 PAGE = 64     # tokens per cache page; PE_PAGE in csrc/common.cuh
 
@@ -275,7 +275,7 @@ def linear_mma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
             out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
         _need(out, "out", None, (M, N))
         epilogue = _EPILOGUE_STORE[out.dtype]
-    lib = core()
+    lib = extras()
     partial = tickets = None
     if lib.pe_linear_mma_splits(N, K) > 1:
         partial = scratch("linear_mma.partial", lib.pe_linear_mma_scratch_bytes(64, N, K), a.device).data_ptr()
@@ -505,7 +505,7 @@ def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torc
     else:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=w.device)
         epilogue = _EPILOGUE_STORE[out.dtype]
-    fn, name = (core().pe_linear_fused, "linear_fused") if M <= FUSED_MAX_ROWS else (core().pe_linear_batch, "linear_batch")
+    fn, name = (core().pe_linear_fused, "linear_fused") if M <= FUSED_MAX_ROWS else (extras().pe_linear_batch, "linear_batch")
     check(fn(_ptr(a), _ptr(norm_of), _ptr(norm_weight), 0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
              w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
              epilogue, M, N, K, status_ptr(w.device), stream_ptr()), name)
@@ -518,7 +518,7 @@ def norm_gate_up_swiglu(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
     I = w_gate_up.shape[0] // 2
     _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
     act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
-    fn = core().pe_norm_gate_up_swiglu if M <= FUSED_MAX_ROWS else core().pe_batch_norm_gate_up_swiglu
+    fn = core().pe_norm_gate_up_swiglu if M <= FUSED_MAX_ROWS else extras().pe_batch_norm_gate_up_swiglu
     check(fn(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps),
              w_gate_up.data_ptr(), act.data_ptr(), M, I, K, status_ptr(x.device), stream_ptr()), "norm_gate_up_swiglu")
     return act
@@ -553,7 +553,7 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
     if M <= FUSED_MAX_ROWS:
         check(core().pe_norm_qkv_rope_store(None, *head, *tail), "norm_qkv_rope_store")
     else:
-        check(core().pe_batch_norm_qkv_rope_store(*head, *tail), "batch_norm_qkv_rope_store")
+        check(extras().pe_batch_norm_qkv_rope_store(*head, *tail), "batch_norm_qkv_rope_store")
     return q
 
 

@@ -11,8 +11,10 @@ from ..csrc import build
 
 P, I, F, LL, ULL = c_void_p, c_int, c_float, c_longlong, c_ulonglong
 
-CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_mma.cu",
-                "linear_fused.cu", "linear_batch.cu", "gemm_tcgen05.cu")
+CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_fused.cu", "gemm_tcgen05.cu")
+# Kernels that no model needs unless it is asked for them: the allocation-free entry point and the split-K product it
+# is built on (linear_mma.cu), and the fused decode products for 17 to 64 rows (linear_batch.cu, off by default).
+EXTRA_SOURCES = ("linear_mma.cu", "linear_batch.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -28,16 +30,19 @@ _SIGNATURES = {
     "pe_attention_generic": [P, I, P, P, P, I, P, I, P, P, I, I, I, I, I, F, P],
     "pe_argmax": [P, P, I, I, P, P],
     "pe_sample": [P, P, I, I, F, I, F, ULL, P, P, P, P, P],
-    "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
-    "pe_linear_mma_splits": [I, I],
     "pe_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, P, P],
     "pe_gemm_tcgen05_rope": [P, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P, P],
     "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
     "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
+    "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
+}
+
+_EXTRA_SIGNATURES = {
+    "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
+    "pe_linear_mma_splits": [I, I],
     "pe_linear_batch": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
     "pe_batch_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
     "pe_batch_norm_qkv_rope_store": [P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
-    "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
 }
 
 _HEAD_DIM_SIGNATURES = {
@@ -78,10 +83,24 @@ def core() -> ctypes.CDLL:
         lib.pe_argmax_scratch_bytes.restype = c_longlong
         lib.pe_sample_scratch_bytes.argtypes = [I, I]
         lib.pe_sample_scratch_bytes.restype = c_longlong
-        lib.pe_linear_mma_scratch_bytes.argtypes = [I, I, I]
-        lib.pe_linear_mma_scratch_bytes.restype = c_longlong
         _core = lib
     return _core
+
+
+_extras = None
+
+
+def extras() -> ctypes.CDLL:
+    """The library of the kernels that are not on a model's default path; compiled at the first call."""
+    global _extras
+    if _extras is None:
+        lib = build.load("extras", EXTRA_SOURCES)
+        declare(lib, _EXTRA_SIGNATURES)
+        lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
+        lib.pe_linear_mma_scratch_bytes.argtypes = [I, I, I]
+        lib.pe_linear_mma_scratch_bytes.restype = c_longlong
+        _extras = lib
+    return _extras
 
 
 def head_dim_sizes() -> range:

@@ -18,8 +18,8 @@ TOO_LARGE, UNSUPPORTED = 10002, 10001
 
 @pytest.fixture(scope="module")
 def static_entry():
-    from pico_engine.ops.library import core
-    fn = core().pe_linear_mma_static                 # the exported symbol; nothing in the package wraps it
+    from pico_engine.ops.library import extras
+    fn = extras().pe_linear_mma_static                 # the exported symbol; nothing in the package wraps it
     P, I = ctypes.c_void_p, ctypes.c_int
     fn.argtypes = [P, P, P, I, P, I, I, I, I, P]
     fn.restype = I
@@ -61,8 +61,8 @@ def test_two_calls_in_a_row_equal_the_ordinary_entry_point(static_entry, M, N, K
 
 
 def test_sizes_beyond_the_fixed_array_are_refused(static_entry):
-    from pico_engine.ops.library import core
-    lib = core()
+    from pico_engine.ops.library import extras
+    lib = extras()
     lib.pe_linear_mma_scratch_bytes.argtypes = [ctypes.c_int] * 3
     lib.pe_linear_mma_scratch_bytes.restype = ctypes.c_longlong
     M, N, K = 64, 1152, 2048                                     # five K ranges of 64 x 1152 sums: 1.4 MiB, the array holds 1 MiB
