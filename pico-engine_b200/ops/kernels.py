@@ -560,6 +560,13 @@ def norm_qkv_rope_store(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, 
 # ---------------------------------------------------------------------------- tcgen05 products for more than 16 rows (bfloat16)
 
 ORIENTATION = {None: 0, "rows": 1, "swapped": 2, "pairs": 3}
+# Orientation "splitk" (csrc/gemm_splitk.cu): rows of w on the lanes, K cut into ranges over a thread-block cluster, for up
+# to 64 rows of a.  Nothing chooses it by itself: measured on a B200 at the Qwen2.5-0.5B widths and 64 rows, in captured
+# graphs, it takes 8.5 / 7.2 / 11.8 / 9.5 us for q/k/v + RoPE, o + residual, gate/up + SwiGLU and down + residual where
+# the library's product with the pass that follows it takes 5.9 / 5.3 / 7.7 / 10.1; at the 7B widths it streams
+# gate/up at 4.6 to 5.0 TB/s (library 5.2).  One thread issues a stage's three TMA copies and another its four MMAs at
+# 150 to 200 cycles an instruction, which is 700 cycles for 24 KB of operands, whatever the accumulators' number.
+SPLITK_MAX_ROWS = 64
 
 
 def gemm_tcgen05_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -588,6 +595,10 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
         out, epilogue = torch.empty(M, N // 2, dtype=torch.bfloat16, device=a.device), 2
     else:
         out, epilogue = torch.empty(M, N, dtype=torch.bfloat16, device=a.device), 0
+    if orientation == "splitk":                  # rows of w on the lanes, K cut over a cluster (up to 64 rows of a)
+        check(extras().pe_gemm_splitk(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
+                                    out.data_ptr(), epilogue, M, N, K, status_ptr(a.device), stream_ptr()), "gemm_splitk")
+        return out
     check(core().pe_gemm_tcgen05(a.data_ptr(), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"),
                                  out.data_ptr(), epilogue, M, N, K, ORIENTATION[orientation], status_ptr(a.device),
                                  stream_ptr()), "gemm_tcgen05")
@@ -608,7 +619,7 @@ def gemm_qkv_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[to
     M, K = a.shape
     N = (n_q + 2 * n_kv) * head_dim
     _need(a, "a", torch.bfloat16); _need(w_qkv, "w_qkv", torch.bfloat16, (N, K))
-    if head_dim not in GEMM_ROPE_HEAD_DIMS:
+    if head_dim not in GEMM_ROPE_HEAD_DIMS and orientation != "splitk":
         raise KernelError(f"head size {head_dim} is not taken by the fused q/k/v product: {GEMM_ROPE_HEAD_DIMS} are")
     if b_qkv is not None:
         _need(b_qkv, "b_qkv", None, (N,))
@@ -624,6 +635,12 @@ def gemm_qkv_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[to
         if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim):
             raise KernelError(f"cache pool must be [pages, {n_kv}, {PAGE}, {head_dim}], not {tuple(k_pool.shape)}")
     q = torch.empty(M, n_q * head_dim, dtype=torch.bfloat16, device=a.device)
+    if orientation == "splitk":
+        check(extras().pe_gemm_splitk_rope(a.data_ptr(), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
+                                         q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
+                                         tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
+                                         1 if store else 0, status_ptr(a.device), stream_ptr()), "gemm_splitk_rope")
+        return q
     check(core().pe_gemm_tcgen05_rope(a.data_ptr(), w_qkv.data_ptr(), _ptr(b_qkv), 0 if b_qkv is None else _code(b_qkv, "b_qkv"),
                                       q.data_ptr(), M, K, n_q, n_kv, head_dim, _ptr(cos), _ptr(sin), tok_pos.data_ptr(),
                                       tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,

@@ -13,8 +13,10 @@ P, I, F, LL, ULL = c_void_p, c_int, c_float, c_longlong, c_ulonglong
 
 CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sampling.cu", "linear_fused.cu", "gemm_tcgen05.cu")
 # Kernels that no model needs unless it is asked for them: the allocation-free entry point and the split-K product it
-# is built on (linear_mma.cu), and the fused decode products for 17 to 64 rows (linear_batch.cu, off by default).
-EXTRA_SOURCES = ("linear_mma.cu", "linear_batch.cu")
+# is built on (linear_mma.cu), and the two kernels for decode steps of 17 to 64 rows that the library's products with
+# this library's small kernels between them still beat (linear_batch.cu: mma.sync with fused prologue and epilogues;
+# gemm_splitk.cu: tcgen05 with K cut over a cluster).
+EXTRA_SOURCES = ("linear_mma.cu", "linear_batch.cu", "gemm_splitk.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -38,6 +40,8 @@ _SIGNATURES = {
 }
 
 _EXTRA_SIGNATURES = {
+    "pe_gemm_splitk": [P, P, P, I, P, I, I, I, I, P, P],
+    "pe_gemm_splitk_rope": [P, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
     "pe_linear_mma": [P, P, P, I, P, I, I, I, I, P, P, P],
     "pe_linear_mma_splits": [I, I],
     "pe_linear_batch": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],

@@ -808,14 +808,19 @@ def test_gemm_tcgen05_swiglu(K, orientation, M, H, I):
     assert got.shape == (M, I) and err < 1.2e-2, (err, at)
 
 
-@pytest.mark.parametrize("orientation", ORIENTATIONS)
+@pytest.mark.parametrize("orientation", ORIENTATIONS + ["splitk"])
 @pytest.mark.parametrize("nq,nkv,hd,H,theta,rotate,M", [(4, 2, 16, 64, 1e4, True, 40), (3, 1, 32, 96, 1e6, True, 70),
                                                          (14, 2, 64, 896, 1e6, True, 200), (28, 4, 128, 3584, 1e6, True, 130),
                                                          (5, 5, 64, 240, 1e4, False, 33), (14, 2, 64, 896, 1e6, True, 64),
-                                                         (14, 2, 64, 896, 1e6, True, 600)])
+                                                         (14, 2, 64, 896, 1e6, True, 600), (5, 1, 48, 200, 1e4, True, 50),
+                                                         (28, 4, 128, 3584, 1e6, True, 47), (3, 1, 32, 96, 1e6, True, 17)])
 def test_gemm_qkv_rope_store(K, orientation, nq, nkv, hd, H, theta, rotate, M):
     """The q/k/v product with bias, rotation and cache write in its epilogue: M tokens of a few sequences of
     unequal lengths that start at unequal places of their (shuffled) pages."""
+    if orientation == "splitk" and M > K.SPLITK_MAX_ROWS:
+        pytest.skip("K cut over a cluster is for up to 64 rows")
+    if orientation != "splitk" and hd not in K.GEMM_ROPE_HEAD_DIMS:
+        pytest.skip("head sizes that are no power of two: only with K cut over a cluster")
     lens, starts, left, i = [], [], M, 0
     while left > 0:
         n = min(left, [1, 37, 64, 9, 100][i % 5])
@@ -856,6 +861,41 @@ def test_gemm_qkv_rope_store(K, orientation, nq, nkv, hd, H, theta, rotate, M):
                                dev(cos) if rotate else None, dev(sin) if rotate else None, dev(pos), dev(row), None, None,
                                None, 0, orientation=orientation)
     assert torch.equal(q, q2) and float(kp.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("M", [17, 32, 33, 64])
+@pytest.mark.parametrize("N,K_", [(1152, 896), (896, 896), (896, 4864), (136, 72), (264, 200), (3584, 3584), (100, 64), (4608, 128)])
+def test_gemm_splitk(K, M, N, K_):
+    """The product for 17 to 64 rows with K cut over a cluster (csrc/gemm_splitk.cu): widths that are no multiple of the
+    128-row tile or of the 64-column block, one to eight ranges."""
+    a, w, b = bf(rnd(M, K_, seed=1)), bf(rnd(N, K_, seed=2, scale=K_ ** -0.5)), bf(rnd(N, seed=3))
+    A, W = dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16))
+    want = a.double() @ w.double().T
+    for bias_dtype in (torch.bfloat16, torch.float32):
+        got = K.gemm_tcgen05(A, W, dev(b.to(bias_dtype)), orientation="splitk")
+        K.check_status("cuda")
+        err, at = rel_err(got.float(), want + b.double())
+        assert got.shape == (M, N) and err < 5e-3, (err, at)
+    x = rnd(M, N, seed=4)
+    got = K.gemm_tcgen05(A, W, accumulate_into=dev(x.clone()), orientation="splitk")
+    K.check_status("cuda")
+    err, at = rel_err(got, x.double() + want)
+    assert err < 2e-5, (err, at)
+    again = K.gemm_tcgen05(A, W, accumulate_into=dev(x.clone()), orientation="splitk")
+    assert torch.equal(got, again)                                  # the ranges are added in a fixed order
+    part = K.gemm_tcgen05(A[:20].contiguous(), W, accumulate_into=dev(x[:20].clone()), orientation="splitk")
+    assert torch.equal(part, got[:20])                              # a row does not depend on its neighbours
+
+
+@pytest.mark.parametrize("M,H,I", [(24, 896, 4864), (64, 896, 4864), (40, 64, 160), (33, 96, 352), (17, 3584, 1000)])
+def test_gemm_splitk_swiglu(K, M, H, I):
+    a, w = bf(rnd(M, H, seed=1)), bf(rnd(2 * I, H, seed=3, scale=H ** -0.5))
+    gu = (a.double() @ w.double().T).to(torch.bfloat16).float()
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    got = K.gemm_tcgen05(dev(a.to(torch.bfloat16)), dev(w.to(torch.bfloat16)), swiglu=True, orientation="splitk")
+    K.check_status("cuda")
+    err, at = rel_err(got.float(), want)
+    assert got.shape == (M, I) and err < 1.2e-2, (err, at)
 
 
 def test_gemm_tcgen05_refuses_what_it_does_not_take(K):
