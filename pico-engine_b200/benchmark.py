@@ -351,6 +351,26 @@ def product_times(engine, rows: int) -> dict:
                               "library": t(lambda: kernels.residual_add(x, torch.mm(a, att.w_o.t())))}
     out["down_residual"] = {"tcgen05": t(lambda: kernels.gemm_tcgen05(act, ffn.w_down, accumulate_into=x)),
                             "library": t(lambda: kernels.residual_add(x, torch.mm(act, ffn.w_down.t())))}
+    if rows <= kernels.SPLITK_MAX_ROWS:
+        # the two kernels for 17 to 64 rows that nothing chooses by itself: K cut over a cluster on tcgen05
+        # (csrc/gemm_splitk.cu), and the mma.sync kernel with the norm in its prologue (csrc/linear_batch.cu; its
+        # counterpart on the library's side has the norm as a kernel of its own)
+        norm1, norm2 = layer.mixer_norm, layer.feed_forward_norm
+        xs = torch.randn(rows, s.hidden, device=dev)
+        out["gate_up_swiglu"]["splitk"] = t(lambda: kernels.gemm_tcgen05(h, ffn.w_gate_up, swiglu=True, orientation="splitk"))
+        out["qkv_rope"] = out.get("qkv_rope", {})
+        out["qkv_rope"]["splitk"] = t(lambda: kernels.gemm_qkv_rope_store(h, att.w_qkv, att.b_qkv, s.n_heads, s.n_kv_heads, s.head_dim,
+                                                                            cos, sin, pos, pos, None, None, None, 0, orientation="splitk"))
+        out["o_proj_residual"]["splitk"] = t(lambda: kernels.gemm_tcgen05(a, att.w_o, accumulate_into=x, orientation="splitk"))
+        out["down_residual"]["splitk"] = t(lambda: kernels.gemm_tcgen05(act, ffn.w_down, accumulate_into=x, orientation="splitk"))
+        if rows > kernels.FUSED_MAX_ROWS and hasattr(norm1, "eps") and hasattr(norm2, "eps"):
+            out["gate_up_swiglu"]["batch_with_norm"] = t(lambda: kernels.norm_gate_up_swiglu(xs, norm2.weight, norm2.eps, ffn.w_gate_up))
+            out["gate_up_swiglu"]["library_with_norm"] = t(lambda: kernels.swiglu(torch.mm(
+                kernels.rmsnorm(xs, norm2.weight, norm2.eps, dt), ffn.w_gate_up.t())))
+            out["qkv_rope"]["batch_with_norm"] = t(lambda: kernels.norm_qkv_rope_store(
+                xs, norm1.weight, norm1.eps, att.w_qkv, att.b_qkv, s.n_heads, s.n_kv_heads, s.head_dim, cos, sin, pos, pos, None, None, None, 0))
+            out["o_proj_residual"]["batch"] = t(lambda: kernels.linear_fused(a, att.w_o, accumulate_into=x))
+            out["down_residual"]["batch"] = t(lambda: kernels.linear_fused(act, ffn.w_down, accumulate_into=x))
     kernels.check_status(dev)
     return out
 
@@ -425,7 +445,7 @@ def main(argv=None) -> None:
         times = product_times(eng, rows)
         record.setdefault("products", {})[str(rows)] = times
         for name, t in times.items():
-            print(f"{rows} rows {name}: tcgen05 {t['tcgen05']:.1f} us, library {t['library']:.1f} us")
+            print(f"{rows} rows {name}: " + ", ".join(f"{k} {v:.1f} us" for k, v in t.items()))
     if args.requests > 0:
         lo, hi = (int(x) for x in args.prompt_lengths.split(","))
         gen = generate_protocol(eng, args.requests, lo, hi, args.n_tokens, args.warmups, args.repetitions, use_graph=not args.no_graph)
